@@ -35,11 +35,15 @@ class KVRequest:
     """Token-indexed storage a mixer asks for.  ``kind`` names a registered storage class
     (``register_cache_kind``); "full": keys are stored by position in pages.
     ``window`` is the number of most recent keys the mixer reads (None: all); with a window
-    the pages that no query can reach any more are given back while the sequence grows."""
+    the pages that no query can reach any more are given back while the sequence grows, except
+    those that hold any of the first ``keep_first`` keys (a window that also keeps the sequence's
+    first tokens).  ``value_dim``: the size of a value row where it differs from a key's."""
     kv_heads: int
     head_dim: int
     kind: str = "full"
     window: Optional[int] = None
+    value_dim: Optional[int] = None
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)
@@ -101,13 +105,14 @@ class PagedGroup:
         self.entries = entries
         if request.window is not None and window_step_tokens is not None:
             # the window's keys and the step's new tokens, both possibly straddling page borders
-            per_slot = pages_for(request.window + window_step_tokens, PAGE) + 1
+            per_slot = pages_for(request.window + window_step_tokens, PAGE) + 1 + pages_for(request.keep_first, PAGE)
             n_pages = max(1, min(n_pages, n_slots * per_slot))
         self.pages = FreeList(n_pages, "page")
         self.blocks_per_seq = blocks_per_seq
         shape = (len(entries), n_pages, request.kv_heads, PAGE, request.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device) if self.stores_values else self.k
+        v_shape = shape[:-1] + (request.value_dim or request.head_dim,)
+        self.v = torch.zeros(v_shape, dtype=dtype, device=device) if self.stores_values else self.k
         # Pageable on purpose: a copy from pageable memory is staged before the call returns,
         # so the host may rewrite a row (a slot that is reused) while an earlier step's copy
         # is still queued on the device.
@@ -128,7 +133,8 @@ class PagedGroup:
             # the first key any query of this step (positions old_length and up) or of a later
             # one reads is old_length - window + 1: whole blocks below it go back to the pool
             keep_from = min(max(0, old_length - self.request.window + 1) // PAGE, len(have))
-            for b in range(self.first_block[slot], keep_from):
+            kept_first = pages_for(self.request.keep_first, PAGE)      # blocks that hold kept first keys stay
+            for b in range(max(self.first_block[slot], kept_first), keep_from):
                 self.pages.give_back(have[b])
                 have[b] = -1
             self.first_block[slot] = max(self.first_block[slot], keep_from)
@@ -163,7 +169,7 @@ class PagedGroup:
         return self.pages.n
 
     def bytes(self) -> int:
-        return self.k.numel() * self.k.element_size() * (2 if self.stores_values else 1)
+        return self.k.numel() * self.k.element_size() + (self.v.numel() * self.v.element_size() if self.stores_values else 0)
 
 
 @register_cache_kind("keys")

@@ -5,7 +5,8 @@ from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, default_schedul
 from .llama import Llama3RopeScaling, LlamaConfig
 from .terolix import TerolixConfig
 from .munadra import MunadraConfig
+from .bededra import BededraConfig
 
 __all__ = ["ConfigError", "config_class", "config_from_dict", "config_from_file", "config_from_folder",
            "known_architectures", "register_architecture", "LayerSpec", "ModelSpec", "PartSpec",
-           "ScheduleEntry", "default_schedule", "Llama3RopeScaling", "LlamaConfig", "TerolixConfig", "MunadraConfig"]
+           "ScheduleEntry", "default_schedule", "Llama3RopeScaling", "LlamaConfig", "TerolixConfig", "MunadraConfig", "BededraConfig"]

@@ -42,6 +42,9 @@ SOURCES: Dict[str, str] = {
     "latent": "latent.cu",
     "attention_latent": "attention_latent.cu",
     "linear_recurrence": "linear_recurrence.cu",
+    "short_conv": "short_conv.cu",
+    "outer_recurrence": "outer_recurrence.cu",
+    "attention_mixed": "attention_mixed.cu",
 }
 HEADERS: List[str] = ["common.cuh", "tcgen05.cuh", "tma_host.cuh", "attention_decode_noalloc.h"]
 

@@ -6,7 +6,7 @@
 
 namespace kl {
 
-enum : int { ACT_XIELU = 0, ACT_GELU_TANH = 1, ACT_SILU = 2 };
+enum : int { ACT_XIELU = 0, ACT_GELU_TANH = 1, ACT_SILU = 2, ACT_RELU2 = 3 };     // relu2: max(z, 0)^2
 
 // xIELU with a_pos = softplus(p) and a_neg = 1/2 + softplus(q) (both made at load, params[0..1]):
 //   z > 0:  a_pos z^2 + z / 2          z <= 0:  a_neg (exp(z) - 1 - z) + z / 2
@@ -15,6 +15,7 @@ enum : int { ACT_XIELU = 0, ACT_GELU_TANH = 1, ACT_SILU = 2 };
 template <bool FAST>
 __device__ __forceinline__ float activate(float z, int kind, float a_pos, float a_neg) {
     if (kind == ACT_XIELU) return z > 0.f ? a_pos * z * z + 0.5f * z : a_neg * ((FAST ? __expf(z) - 1.0f : expm1f(z)) - z) + 0.5f * z;
+    if (kind == ACT_RELU2) { const float r = fmaxf(z, 0.f); return r * r; }
     if (kind == ACT_GELU_TANH) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
     return z / (1.0f + (FAST ? __expf(-z) : expf(-z)));
 }
@@ -77,7 +78,7 @@ using namespace kl;
 KL_API int kl_activation(const void* x, long long ld_x, void* out, long long ld_out, int tokens, int n, int kind,
                          const float* params, int dtype, cudaStream_t stream) {
     if (tokens <= 0 || n <= 0) return KL_OK;
-    if (kind < ACT_XIELU || kind > ACT_SILU || (kind == ACT_XIELU && params == nullptr)) return KL_ERR_BAD_SIZE;
+    if (kind < ACT_XIELU || kind > ACT_RELU2 || (kind == ACT_XIELU && params == nullptr)) return KL_ERR_BAD_SIZE;
     const int threads = 256;
     if (dtype != KL_F32 && dtype != KL_BF16) return KL_ERR_BAD_DTYPE;
     const int v = dtype == KL_F32 ? 4 : 8;

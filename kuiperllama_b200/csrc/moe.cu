@@ -23,9 +23,10 @@ constexpr int MOE_MAX_EXPERTS = 32 * MOE_MAX_PER_LANE;
 
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ logits, long long ld, int tokens, int experts, int top, int renormalise,
-                 int* __restrict__ choice, float* __restrict__ weight) {
+                 int groups, int keep_groups, float renorm_eps, int* __restrict__ choice, float* __restrict__ weight) {
     pdl_launch_dependents();
     pdl_wait();
+    __shared__ float group_best[4][MOE_MAX_EXPERTS];
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (t >= tokens) return;
@@ -47,6 +48,37 @@ moe_route_kernel(const float* __restrict__ logits, long long ld, int tokens, int
         sum += e < experts ? s[i] : 0.f;
     }
     sum = warp_sum(sum);
+    if (groups > 1 && keep_groups < groups) {
+        // Experts form `groups` equal groups of neighbours; a group's score is its largest score, and only the experts
+        // of the `keep_groups` best groups (the lower index among equals) stay in the choice.
+        float* gb = group_best[threadIdx.x >> 5];
+        const int per = experts / groups;
+        for (int g = lane; g < groups; g += 32) gb[g] = -1.f;
+        __syncwarp();
+        for (int g = 0; g < groups; ++g) {
+            float b = -1.f;
+#pragma unroll
+            for (int i = 0; i < MOE_MAX_PER_LANE; ++i) {
+                const int e = lane + 32 * i;
+                if (e < experts && e / per == g) b = fmaxf(b, s[i]);
+            }
+            b = warp_max(b);
+            if (lane == 0) gb[g] = b;
+        }
+        __syncwarp();
+        // rank of every group: how many groups come before it (a larger score, or an equal one with a lower index)
+#pragma unroll
+        for (int i = 0; i < MOE_MAX_PER_LANE; ++i) {
+            const int e = lane + 32 * i;
+            if (e < experts) {
+                const int g = e / per;
+                const float mine_b = gb[g];
+                int before = 0;
+                for (int o = 0; o < groups; ++o) before += (gb[o] > mine_b || (gb[o] == mine_b && o < g)) ? 1 : 0;
+                if (before >= keep_groups) s[i] = -1.f;
+            }
+        }
+    }
     float chosen_sum = 0.f, mine = 0.f;
     int mine_e = 0;
     for (int k = 0; k < top; ++k) {
@@ -73,7 +105,7 @@ moe_route_kernel(const float* __restrict__ logits, long long ld, int tokens, int
     }
     // weights: the softmax scores, or those divided by the chosen ones' sum
     __syncwarp();
-    const float denom = renormalise ? chosen_sum : sum;
+    const float denom = renormalise ? chosen_sum + renorm_eps * sum : sum;      // scores s = exp / sum: s_k / (sum of chosen s + eps)
     for (int kk = lane; kk < top; kk += 32) weight[(size_t)t * top + kk] = weight[(size_t)t * top + kk] / denom;
 }
 
@@ -167,11 +199,13 @@ KL_API int kl_moe_gather(const void* x, long long ld, const int* list_rows, int 
     return KL_OK;
 }
 
-KL_API int kl_moe_route(const float* logits, long long ld, int tokens, int experts, int top, int renormalise, int* choice,
-                        float* weight, cudaStream_t stream) {
+KL_API int kl_moe_route(const float* logits, long long ld, int tokens, int experts, int top, int renormalise, int groups,
+                        int keep_groups, float renorm_eps, int* choice, float* weight, cudaStream_t stream) {
     if (tokens <= 0) return KL_OK;
     if (experts <= 0 || experts > MOE_MAX_EXPERTS || top <= 0 || top > experts) return KL_ERR_BAD_SIZE;
-    launch_kernel(moe_route_kernel, (tokens + 3) / 4, 128, 0, stream, logits, ld, tokens, experts, top, renormalise, choice, weight);
+    if (groups < 1 || experts % groups || keep_groups < 1 || keep_groups > groups || top > keep_groups * (experts / groups)) return KL_ERR_BAD_SIZE;
+    launch_kernel(moe_route_kernel, (tokens + 3) / 4, 128, 0, stream, logits, ld, tokens, experts, top, renormalise, groups, keep_groups,
+                  renorm_eps, choice, weight);
     KL_LAUNCH_CHECK();
     return KL_OK;
 }

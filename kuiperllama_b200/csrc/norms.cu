@@ -241,7 +241,8 @@ norm_chain_kernel(float* __restrict__ residual, const T* __restrict__ delta, lon
 template <typename T>
 __global__ void __launch_bounds__(128)
 head_rmsnorm_gate_kernel(const float* __restrict__ x, const T* __restrict__ gate, long long gate_ld, const float* __restrict__ w,
-                         T* __restrict__ out, int tokens, int heads, int dim, float eps) {
+                         T* __restrict__ out, long long out_ld, float out_scale, int tokens, int heads, int dim, float eps, int gate_first,
+                         int wide_weight) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31;
@@ -249,17 +250,81 @@ head_rmsnorm_gate_kernel(const float* __restrict__ x, const T* __restrict__ gate
     if (item >= (long long)tokens * heads) return;
     const int t = (int)(item / heads), h = (int)(item - (long long)t * heads);
     const float* xr = x + ((size_t)t * heads + h) * dim;
+    const T* g = gate ? gate + (size_t)t * gate_ld + (size_t)h * dim : nullptr;
+    const float* wr = w != nullptr ? w + (wide_weight ? (size_t)h * dim : 0) : nullptr;
+    T* o = out + (size_t)t * out_ld + (size_t)h * dim;
+    if (gate_first && g != nullptr) {
+        // the gate comes before the norm: y = x silu(g), then y / rms(y) * w
+        float ss = 0.f;
+        for (int i = lane; i < dim; i += 32) {
+            const float a = to_f32(g[i]);
+            const float y = xr[i] * (a / (1.0f + expf(-a)));
+            ss += y * y;
+        }
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+        for (int i = lane; i < dim; i += 32) {
+            const float a = to_f32(g[i]);
+            float y = xr[i] * (a / (1.0f + expf(-a))) * inv;
+            if (wr != nullptr) y *= wr[i];
+            o[i] = from_f32<T>(y * out_scale);
+        }
+        return;
+    }
     float ss = 0.f;
     for (int i = lane; i < dim; i += 32) ss += xr[i] * xr[i];
     ss = warp_sum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
-    const T* g = gate ? gate + (size_t)t * gate_ld + (size_t)h * dim : nullptr;
-    T* o = out + ((size_t)t * heads + h) * dim;
     for (int i = lane; i < dim; i += 32) {
         float y = xr[i] * inv;
-        if (w != nullptr) y *= w[i];
+        if (wr != nullptr) y *= wr[i];
         if (g != nullptr) { const float a = to_f32(g[i]); y *= a / (1.0f + expf(-a)); }
-        o[i] = from_f32<T>(y);
+        o[i] = from_f32<T>(y * out_scale);
+    }
+}
+
+// The norms of a block whose two sublayers read the same stream: x = residual + (d1 + d2) (each delta rows in the
+// compute dtype or float32 pieces, or absent), written back; one root mean square; out1 = x / rms * w1 and
+// out2 = x / rms * w2 (out2 optional).  With `rows` only those rows are read, into out1[0..), and the stream stays.
+struct PairDelta {
+    const void* rows; long long ld;          // compute dtype [n, hidden], or null
+    const float* pieces; int n_pieces; long long piece_stride;   // float32 [S, n, hidden], or null
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+pair_rmsnorm_kernel(float* __restrict__ residual, const PairDelta d1, const PairDelta d2, const float* __restrict__ w1,
+                    const float* __restrict__ w2, float eps, T* __restrict__ out1, T* __restrict__ out2, const int* __restrict__ rows,
+                    int hidden) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float xrow[];
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const size_t row = rows != nullptr ? (size_t)rows[r] : (size_t)r;
+    float* x = residual + row * hidden;
+    const bool has = d1.rows != nullptr || d1.pieces != nullptr || d2.rows != nullptr || d2.pieces != nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = x[i];
+        if (has) {
+            float add = 0.f;
+            if (d1.rows != nullptr) add += to_f32(((const T*)d1.rows)[row * d1.ld + i]);
+            for (int p = 0; p < d1.n_pieces; ++p) add += d1.pieces[(size_t)p * d1.piece_stride + row * hidden + i];
+            if (d2.rows != nullptr) add += to_f32(((const T*)d2.rows)[row * d2.ld + i]);
+            for (int p = 0; p < d2.n_pieces; ++p) add += d2.pieces[(size_t)p * d2.piece_stride + row * hidden + i];
+            v += add;
+            if (rows == nullptr) x[i] = v;
+        }
+        xrow[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = xrow[i] * inv;
+        if (out1 != nullptr) out1[(size_t)r * hidden + i] = from_f32<T>(v * w1[i]);
+        if (out2 != nullptr) out2[(size_t)r * hidden + i] = from_f32<T>(v * w2[i]);
     }
 }
 
@@ -324,18 +389,42 @@ KL_API int kl_norm_chain(float* residual, const void* delta, long long delta_ld,
     return KL_OK;
 }
 
-KL_API int kl_head_rmsnorm_gate(const float* x, const void* gate, long long gate_ld, const float* w, void* out, int tokens,
-                                int heads, int dim, float eps, int dtype, cudaStream_t stream) {
+KL_API int kl_head_rmsnorm_gate(const float* x, const void* gate, long long gate_ld, const float* w, void* out, long long out_ld,
+                                float out_scale, int tokens, int heads, int dim, float eps, int gate_first, int wide_weight, int dtype,
+                                cudaStream_t stream) {
     if (tokens <= 0 || heads <= 0) return KL_OK;
     if (dim <= 0) return KL_ERR_BAD_SIZE;
     const long long items = (long long)tokens * heads;
     const int blocks = (int)((items + 3) / 4);
     if (dtype == KL_F32)
-        launch_kernel(head_rmsnorm_gate_kernel<float>, blocks, 128, 0, stream, x, (const float*)gate, gate_ld, w, (float*)out, tokens, heads, dim, eps);
+        launch_kernel(head_rmsnorm_gate_kernel<float>, blocks, 128, 0, stream, x, (const float*)gate, gate_ld, w, (float*)out, out_ld, out_scale, tokens, heads, dim, eps, gate_first, wide_weight);
     else if (dtype == KL_BF16)
-        launch_kernel(head_rmsnorm_gate_kernel<bf16>, blocks, 128, 0, stream, x, (const bf16*)gate, gate_ld, w, (bf16*)out, tokens, heads, dim, eps);
+        launch_kernel(head_rmsnorm_gate_kernel<bf16>, blocks, 128, 0, stream, x, (const bf16*)gate, gate_ld, w, (bf16*)out, out_ld, out_scale, tokens, heads, dim, eps, gate_first, wide_weight);
     else
         return KL_ERR_BAD_DTYPE;
+    KL_LAUNCH_CHECK();
+    return KL_OK;
+}
+
+// d*_rows: compute dtype; d*_pieces: float32 [S, n, hidden].  out2 may be null; with `rows` the stream is not written.
+KL_API int kl_pair_rmsnorm(float* residual, const void* d1_rows, long long d1_ld, const float* d1_pieces, int d1_n, long long d1_stride,
+                           const void* d2_rows, long long d2_ld, const float* d2_pieces, int d2_n, long long d2_stride,
+                           const float* w1, const float* w2, float eps, void* out1, void* out2, const int* rows, int n_rows, int hidden,
+                           int dtype, cudaStream_t stream) {
+    if (n_rows <= 0) return KL_OK;
+    if (hidden <= 0 || hidden > 48 * 1024 || (out1 != nullptr && w1 == nullptr) || (out2 != nullptr && w2 == nullptr)) return KL_ERR_BAD_SIZE;
+    PairDelta a{d1_rows, d1_ld, d1_pieces, d1_pieces ? d1_n : 0, d1_stride};
+    PairDelta b{d2_rows, d2_ld, d2_pieces, d2_pieces ? d2_n : 0, d2_stride};
+    const size_t smem = (size_t)hidden * sizeof(float);
+    if (dtype == KL_F32) {
+        if (smem > 48 * 1024) KL_CUDA(cudaFuncSetAttribute(pair_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        launch_kernel(pair_rmsnorm_kernel<float>, n_rows, 256, smem, stream, residual, a, b, w1, w2, eps, (float*)out1, (float*)out2, rows, hidden);
+    } else if (dtype == KL_BF16) {
+        if (smem > 48 * 1024) KL_CUDA(cudaFuncSetAttribute(pair_rmsnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        launch_kernel(pair_rmsnorm_kernel<bf16>, n_rows, 256, smem, stream, residual, a, b, w1, w2, eps, (bf16*)out1, (bf16*)out2, rows, hidden);
+    } else {
+        return KL_ERR_BAD_DTYPE;
+    }
     KL_LAUNCH_CHECK();
     return KL_OK;
 }

@@ -173,7 +173,7 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
 # --------------------------------------------------------------------------- norm chains, activations, gates
 
 NORM_KINDS = {"layernorm": 0, "rmsnorm": 1, "none": 2}      # "none": the rows themselves in the compute dtype
-ACTIVATIONS = {"xielu": 0, "gelu_tanh": 1, "silu": 2}
+ACTIVATIONS = {"xielu": 0, "gelu_tanh": 1, "silu": 2, "relu2": 3}      # relu2: max(z, 0)^2
 
 
 def _columns(t: Optional[torch.Tensor], n: int, width: int, name: str) -> None:
@@ -223,19 +223,58 @@ def norm_chain(residual: torch.Tensor, delta: Optional[torch.Tensor], out: Optio
 
 
 def head_rmsnorm_gate(x: torch.Tensor, gate: Optional[torch.Tensor], weight: Optional[torch.Tensor], out: torch.Tensor,
-                      heads: int, dim: int, eps: float) -> None:
+                      heads: int, dim: int, eps: float, gate_first: bool = False, out_scale: float = 1.0) -> None:
     """out[t, h, :] = x[t, h, :] / sqrt(mean(x[t, h, :]^2) + eps) * weight * silu(gate[t, h, :]); x float32
-    [tokens, heads * dim], gate (compute dtype, any row stride) and weight (float32 [dim]) optional."""
+    [tokens, heads * dim], gate (compute dtype, any row stride) and weight (float32 [dim], or [heads * dim]: a weight
+    per channel) optional.  ``gate_first``: the gate comes before the norm, out = norm(x * silu(gate)) * weight.  ``out`` may
+    be a column slice of a wider matrix; the result is multiplied by ``out_scale`` (in 32 bits, before it is rounded)."""
     _cuda(x, gate, weight, out)
     n = x.shape[0]
     _need(x.dtype == torch.float32 and x.is_contiguous() and x.shape[1] == heads * dim, "head_rmsnorm_gate: x")
-    _need(out.is_contiguous() and tuple(out.shape) == (n, heads * dim), "head_rmsnorm_gate: out")
+    _columns(out, n, heads * dim, "head_rmsnorm_gate: out")
     _columns(gate, n, heads * dim, "head_rmsnorm_gate: gate")
     _need(gate is None or gate.dtype == out.dtype, "head_rmsnorm_gate: gate dtype")
-    _need(weight is None or (weight.dtype == torch.float32 and weight.numel() == dim and weight.is_contiguous()), "head_rmsnorm_gate: weight")
+    _need(weight is None or (weight.dtype == torch.float32 and weight.numel() in (dim, heads * dim) and weight.is_contiguous()),
+          "head_rmsnorm_gate: weight")
+    wide = weight is not None and weight.numel() == heads * dim and heads > 1
     _check(lib("norms").kl_head_rmsnorm_gate(_ptr(x), _ptr(gate), ctypes.c_longlong(gate.stride(0) if gate is not None else 0),
-                                             _ptr(weight), _ptr(out), n, heads, dim, ctypes.c_float(eps), dtype_code(out.dtype),
-                                             _stream()), "head_rmsnorm_gate")
+                                             _ptr(weight), _ptr(out), ctypes.c_longlong(out.stride(0)), ctypes.c_float(out_scale), n, heads, dim,
+                                             ctypes.c_float(eps), int(bool(gate_first)), int(wide),
+                                             dtype_code(out.dtype), _stream()), "head_rmsnorm_gate")
+
+
+def pair_rmsnorm(residual: torch.Tensor, deltas, w1: Optional[torch.Tensor], w2: Optional[torch.Tensor], out1: Optional[torch.Tensor],
+                 out2: Optional[torch.Tensor], eps: float, rows: Optional[torch.Tensor] = None, dtype: Optional[torch.dtype] = None) -> None:
+    """x = residual + (d1 + d2), written back unless ``rows``; out1 = x / rms(x) * w1, out2 = x / rms(x) * w2 (one root mean
+    square for both).  ``deltas``: up to two tensors, each [n, hidden] in the compute dtype (any row stride) or float32
+    pieces [S, n, hidden]; outputs may be None."""
+    deltas = [d for d in (deltas or ()) if d is not None]
+    _need(len(deltas) <= 2, "pair_rmsnorm: at most two deltas")
+    _cuda(residual, w1, w2, out1, out2, rows, *deltas)
+    _i32(rows, "rows")
+    hidden = residual.shape[-1]
+    n = rows.numel() if rows is not None else residual.shape[0]
+    _need(residual.dtype == torch.float32 and residual.is_contiguous(), "pair_rmsnorm: the residual stream is float32")
+    if dtype is None:
+        dtype = next((t.dtype for t in (out1, out2) if t is not None), None) or next((d.dtype for d in deltas if d.dim() == 2), torch.float32)
+    args = []
+    for d in deltas + [None] * (2 - len(deltas)):
+        if d is None:
+            args += [ctypes.c_void_p(0), ctypes.c_longlong(0), ctypes.c_void_p(0), 0, ctypes.c_longlong(0)]
+        elif d.dim() == 3:
+            _need(d.dtype == torch.float32 and d.is_contiguous() and tuple(d.shape[1:]) == tuple(residual.shape),
+                  "pair_rmsnorm: pieces must be float32 [S, rows, hidden]")
+            args += [ctypes.c_void_p(0), ctypes.c_longlong(0), _ptr(d), d.shape[0], ctypes.c_longlong(d.shape[1] * d.shape[2])]
+        else:
+            _need(d.dtype == dtype and d.dim() == 2 and d.shape[1] == hidden and d.stride(1) == 1 and d.shape[0] >= residual.shape[0],
+                  "pair_rmsnorm: a delta must be [rows, hidden] in the compute dtype")
+            args += [_ptr(d), ctypes.c_longlong(d.stride(0)), ctypes.c_void_p(0), 0, ctypes.c_longlong(0)]
+    for w, o in ((w1, out1), (w2, out2)):
+        _need(w is None or (w.dtype == torch.float32 and w.is_contiguous() and w.numel() == hidden), "pair_rmsnorm: float32 [hidden] weights")
+        _need(o is None or (w is not None and o.is_contiguous() and o.dtype == dtype and o.shape[-1] == hidden and o.shape[0] >= n),
+              "pair_rmsnorm: output shape")
+    _check(lib("norms").kl_pair_rmsnorm(_ptr(residual), *args, _ptr(w1), _ptr(w2), ctypes.c_float(eps), _ptr(out1), _ptr(out2), _ptr(rows),
+                                        n, hidden, dtype_code(dtype), _stream()), "pair_rmsnorm")
 
 
 def activation(x: torch.Tensor, out: torch.Tensor, kind: str, params: Optional[torch.Tensor] = None) -> None:
@@ -475,17 +514,22 @@ def grouped_gemv(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, a_rows: Op
 MOE_MAX_EXPERTS = 256          # equals MOE_MAX_EXPERTS in moe.cu
 
 
-def moe_route(logits: torch.Tensor, top: int, renormalise: bool = False):
+def moe_route(logits: torch.Tensor, top: int, renormalise: bool = False, groups: int = 1, keep_groups: int = 1,
+              renorm_eps: float = 0.0):
     """(choice int32 [tokens, top], weight float32 [tokens, top]) from float32 router logits [tokens, experts]:
-    softmax over all experts, the ``top`` largest, their scores (divided by their sum if ``renormalise``)."""
+    softmax over all experts, the ``top`` largest, their scores (divided by their sum + ``renorm_eps`` if ``renormalise``).
+    With ``groups`` > 1 the experts form that many equal groups of neighbours, a group's score is its largest score, and
+    only experts of the ``keep_groups`` best groups can be chosen."""
     _cuda(logits)
     n, E = logits.shape
     _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "moe_route: float32 logits")
     _need(0 < top <= E <= MOE_MAX_EXPERTS, f"moe_route: {top} of {E} experts (at most {MOE_MAX_EXPERTS})")
     choice = torch.empty((n, top), dtype=torch.int32, device=logits.device)
     weight = torch.empty((n, top), dtype=torch.float32, device=logits.device)
-    _check(lib("moe").kl_moe_route(_ptr(logits), ctypes.c_longlong(logits.stride(0)), n, E, top, int(bool(renormalise)), _ptr(choice),
-                                   _ptr(weight), _stream()), "moe_route")
+    _need(groups >= 1 and E % groups == 0 and 1 <= keep_groups <= groups and top <= keep_groups * (E // groups),
+          f"moe_route: {groups} groups of which {keep_groups} are kept do not hold {top} of {E} experts")
+    _check(lib("moe").kl_moe_route(_ptr(logits), ctypes.c_longlong(logits.stride(0)), n, E, top, int(bool(renormalise)), int(groups),
+                                   int(keep_groups), ctypes.c_float(renorm_eps), _ptr(choice), _ptr(weight), _stream()), "moe_route")
     return choice, weight
 
 
@@ -692,6 +736,133 @@ def linear_scan(gates: torch.Tensor, block: int, proj: torch.Tensor, y_col: int,
         _ptr(gates), block, _ptr(proj), ctypes.c_longlong(proj.stride(0)), y_col, x_col, _ptr(y_bias), _ptr(x_bias), taps, _ptr(state),
         ctypes.c_longlong(state.stride(0)), _ptr(step.cu_tokens), _ptr(step.seq_slots), _ptr(step.seq_new), step.n_seqs, step.max_new,
         width, _ptr(out), _ptr(scratch), LINEAR_SCAN_CHUNK, dtype_code(proj.dtype), _stream()), "linear_scan", launches)
+
+
+# --------------------------------------------------------------------------- short convolutions, matrix-state recurrences
+
+SHORT_CONV_MAX_TAPS = 16         # equals SC_MAX_TAPS in short_conv.cu
+
+
+def short_conv(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor, step, out: torch.Tensor,
+               add_input: bool = False, silu: bool = False, update_state: bool = True) -> None:
+    """out[t, c] = act((x[t, c] if add_input) + bias[c] + sum_j weight[c, j] * x[t - (taps - 1) + j, c]) over a ragged step;
+    inputs before the step come from ``state`` float32 [slots, >= (taps - 1) * channels] (the last taps - 1 inputs, oldest
+    first; zeros in a fresh slot), which moves on unless ``update_state`` is False.  ``x`` [rows, channels] in the compute
+    dtype (any row stride); ``out`` in the compute dtype or float32; act = SiLU if ``silu``."""
+    _cuda(x, weight, bias, state, out)
+    C, taps = weight.shape
+    _need(weight.dtype == torch.float32 and weight.is_contiguous() and 1 <= taps <= SHORT_CONV_MAX_TAPS, "short_conv: weight [channels, taps]")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == C), "short_conv: bias")
+    _columns(x, step.n_tokens, C, "short_conv: x"); _columns(out, step.n_tokens, C, "short_conv: out")
+    _need(out.dtype in (x.dtype, torch.float32), "short_conv: the output is float32 or in the input's dtype")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1 and state.shape[1] >= (taps - 1) * C, "short_conv: state")
+    _check(lib("short_conv").kl_short_conv(
+        _ptr(x), ctypes.c_longlong(x.stride(0)), _ptr(weight), _ptr(bias), taps, _ptr(state), ctypes.c_longlong(state.stride(0)),
+        _ptr(step.cu_tokens), _ptr(step.seq_slots), step.n_seqs, step.max_new, C, int(bool(add_input)), int(bool(silu)), _ptr(out),
+        ctypes.c_longlong(out.stride(0)), int(out.dtype == torch.float32), int(bool(update_state)), dtype_code(x.dtype), _stream()),
+        "short_conv", 2 if update_state and taps > 1 else 1)
+
+
+def decay_softplus(raw: torch.Tensor, bias: torch.Tensor, A_log: torch.Tensor, n_rows: int, dt: torch.Tensor, a: torch.Tensor) -> None:
+    """dt = softplus(raw + bias) and a = exp(-exp(A_log) * dt) per (row, head), float32 [rows, heads]; ``raw`` [rows, heads] in the
+    compute dtype (any row stride)."""
+    _cuda(raw, bias, A_log, dt, a)
+    heads = bias.numel()
+    _columns(raw, n_rows, heads, "decay_softplus: raw")
+    for t in (bias, A_log):
+        _need(t.dtype == torch.float32 and t.is_contiguous() and t.numel() == heads, "decay_softplus: per-head vectors")
+    for t in (dt, a):
+        _need(t.dtype == torch.float32 and t.is_contiguous() and t.shape[0] >= n_rows and t.shape[1] == heads, "decay_softplus: outputs")
+    _check(lib("outer_recurrence").kl_decay_softplus(_ptr(raw), ctypes.c_longlong(raw.stride(0)), 0, dtype_code(raw.dtype), _ptr(bias),
+                                                     _ptr(A_log), n_rows, heads, _ptr(dt), _ptr(a), _stream()), "decay_softplus")
+
+
+def decay_lowrank(r1: torch.Tensor, W2: torch.Tensor, b: Optional[torch.Tensor], tau: float, n_rows: int, a: torch.Tensor) -> None:
+    """a = sigmoid(z)^(1 / tau), z = W2 r1 + b, float32 [rows, channels]; ``r1`` [rows, rank] in the compute dtype (any row
+    stride), ``W2`` float32 [channels, rank]."""
+    _cuda(r1, W2, b, a)
+    C, rank = W2.shape
+    _columns(r1, n_rows, rank, "decay_lowrank: r1")
+    _need(W2.dtype == torch.float32 and W2.is_contiguous(), "decay_lowrank: W2")
+    _need(b is None or (b.dtype == torch.float32 and b.is_contiguous() and b.numel() == C), "decay_lowrank: bias")
+    _need(a.dtype == torch.float32 and a.is_contiguous() and a.shape[0] >= n_rows and a.shape[1] == C, "decay_lowrank: out")
+    _check(lib("outer_recurrence").kl_decay_lowrank(_ptr(r1), ctypes.c_longlong(r1.stride(0)), 0, rank, _ptr(W2), _ptr(b),
+                                                    ctypes.c_float(tau), n_rows, C, _ptr(a), dtype_code(r1.dtype), _stream()), "decay_lowrank")
+
+
+def outer_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch.Tensor, state: torch.Tensor, y: torch.Tensor, step,
+                     heads: int, groups: int, N: int, P: int, c: Optional[torch.Tensor] = None, skip: Optional[torch.Tensor] = None,
+                     q_scale: float = 1.0) -> None:
+    """S_t = diag(a_t) S_(t-1) + (c_t k_t) v_t^T and y_t = S_t^T (q_scale q_t) + skip v_t per head over a ragged step, from and
+    into ``state`` float32 [slots, >= heads * N * P] (S as [heads, N, P]).  ``q``, ``k`` [rows, groups * N] and ``v``
+    [rows, heads * P] share one dtype (float32 or the compute dtype) and may be column slices; ``a`` float32 [rows, heads]
+    (one decay per head) or [rows, heads * N] (one per row of S); ``c`` float32 [rows, heads] or None; ``skip`` float32
+    [heads] or None; ``y`` float32 [rows, heads * P]."""
+    _cuda(q, k, v, a, state, y, c, skip)
+    n = step.n_tokens
+    _columns(q, n, groups * N, "outer_recurrence: q"); _columns(k, n, groups * N, "outer_recurrence: k")
+    _columns(v, n, heads * P, "outer_recurrence: v")
+    _need(q.dtype == k.dtype == v.dtype, "outer_recurrence: q, k and v share a dtype")
+    _need(a.dtype == torch.float32 and a.dim() == 2 and a.stride(1) == 1 and a.shape[0] >= n and a.shape[1] in (heads, heads * N),
+          "outer_recurrence: a is float32 [rows, heads] or [rows, heads * N]")
+    per_row = a.shape[1] == heads * N and N > 1
+    _need(c is None or (c.dtype == torch.float32 and c.dim() == 2 and c.stride(1) == 1 and c.shape[0] >= n and c.shape[1] == heads),
+          "outer_recurrence: c")
+    _need(skip is None or (skip.dtype == torch.float32 and skip.is_contiguous() and skip.numel() == heads), "outer_recurrence: skip")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1 and state.shape[1] >= heads * N * P, "outer_recurrence: state")
+    _need(y.dtype == torch.float32 and y.dim() == 2 and y.stride(1) == 1 and y.shape[0] >= n and y.shape[1] == heads * P, "outer_recurrence: y")
+    _need(heads % groups == 0 and N <= 1024, "outer_recurrence: heads in equal groups, at most 1,024 rows of state")
+    _check(lib("outer_recurrence").kl_outer_recurrence(
+        _ptr(q), ctypes.c_longlong(q.stride(0)), 0, _ptr(k), ctypes.c_longlong(k.stride(0)), 0, _ptr(v), ctypes.c_longlong(v.stride(0)), 0,
+        _ptr(a), ctypes.c_longlong(a.stride(0)), int(per_row), _ptr(c), ctypes.c_longlong(c.stride(0) if c is not None else 0), _ptr(skip),
+        _ptr(state), ctypes.c_longlong(state.stride(0)), _ptr(y), ctypes.c_longlong(y.stride(0)), _ptr(step.cu_tokens),
+        _ptr(step.seq_slots), step.n_seqs, heads, groups, N, P, ctypes.c_float(q_scale), dtype_code(q.dtype), _stream()), "outer_recurrence")
+
+
+# --------------------------------------------------------------------------- attention with mixed heads
+
+def kv_append(src: torch.Tensor, k_col: int, v_col: int, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+              step, kv_heads: int, dim: int, vdim: int) -> None:
+    """Keys (``src[:, k_col:]``, kv_heads * dim wide) and values (``src[:, v_col:]``, kv_heads * vdim wide) of the step's tokens
+    into the paged cache, as they are (no rotation)."""
+    _cuda(src, k_cache, v_cache, block_table)
+    _i32(block_table, "block_table")
+    n = step.n_tokens
+    _need(src.dim() == 2 and src.stride(1) == 1 and src.shape[0] >= n and k_col + kv_heads * dim <= src.shape[1]
+          and v_col + kv_heads * vdim <= src.shape[1], "kv_append: projections")
+    _need(k_cache.dtype == v_cache.dtype == src.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+          and tuple(k_cache.shape[1:]) == (kv_heads, PAGE, dim) and tuple(v_cache.shape[1:]) == (kv_heads, PAGE, vdim), "kv_append: cache layout")
+    _check(lib("attention_mixed").kl_kv_append(_ptr(src), ctypes.c_longlong(src.stride(0)), k_col, v_col, _ptr(k_cache), _ptr(v_cache),
+                                               _ptr(block_table), block_table.shape[1], _ptr(step.positions), _ptr(step.token_slot), n,
+                                               kv_heads, dim, vdim, dtype_code(src.dtype), _stream()), "kv_append")
+
+
+def attention_mixed(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                    block_table: torch.Tensor, step, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, softcap: float = 0.0,
+                    r1: Optional[torch.Tensor] = None, r2: Optional[torch.Tensor] = None, talk: Optional[torch.Tensor] = None,
+                    window: int = 0, keep_first: int = 0, out_scale: float = 1.0) -> None:
+    """Attention of every token of ``step`` over its sequence's cache with soft-capped scores, a distance bias
+    r1_h ln(1 + r2_h (i - j)) taken off, a sliding window that also keeps the first ``keep_first`` keys, the heads' softmax
+    weights mixed by ``talk`` [heads, heads], and head h's result times out_scale * sigmoid(gate[t, h]) (see
+    attention_mixed.cu).  ``q`` [rows, heads * dim], ``gate`` [rows, heads], ``out`` [rows, heads * vdim]: the compute dtype,
+    any row stride."""
+    _cuda(q, gate, out, k_cache, v_cache, block_table, r1, r2, talk)
+    _i32(block_table, "block_table")
+    n = step.n_tokens
+    _columns(q, n, heads * dim, "attention_mixed: q"); _columns(out, n, heads * vdim, "attention_mixed: out")
+    _columns(gate, n, heads, "attention_mixed: gate")
+    _need(q.dtype == out.dtype == k_cache.dtype == v_cache.dtype and (gate is None or gate.dtype == q.dtype), "attention_mixed: dtypes differ")
+    _need(k_cache.is_contiguous() and v_cache.is_contiguous() and tuple(k_cache.shape[1:]) == (kv_heads, PAGE, dim)
+          and tuple(v_cache.shape[1:]) == (kv_heads, PAGE, vdim), "attention_mixed: cache layout")
+    for t, count in ((r1, heads), (r2, heads), (talk, heads * heads)):
+        _need(t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == count), "attention_mixed: float32 per-head tensors")
+    _need((r1 is None) == (r2 is None), "attention_mixed: the distance bias needs both of its numbers")
+    _need(heads % kv_heads == 0, "attention_mixed: heads must be a multiple of kv heads")
+    _check(lib("attention_mixed").kl_attention_mixed(
+        _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(gate), ctypes.c_longlong(gate.stride(0) if gate is not None else 0), _ptr(out),
+        ctypes.c_longlong(out.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(step.positions),
+        _ptr(step.token_slot), n, heads, kv_heads, dim, vdim, ctypes.c_float(scale), ctypes.c_float(softcap or 0.0), _ptr(r1), _ptr(r2),
+        _ptr(talk), int(window or 0), int(keep_first or 0), ctypes.c_float(out_scale), dtype_code(q.dtype), _stream()), "attention_mixed")
 
 
 # --------------------------------------------------------------------------- matrix products

@@ -1,0 +1,235 @@
+// A linear recurrence whose state is a matrix per head, fed by outer products:
+//
+//   S_t = diag(a_t) S_(t-1) + (c_t k_t) v_t^T        S: [N, P] per head, float32, from the slot's state (zero in a fresh slot)
+//   y_t = S_t^T q_t + D v_t                           y: [P] per head, float32
+//
+// a_t is one number per (token, head) (a state-space layer: exp(-exp(A_log) dt), with c_t = dt, k = B, q = C, v = x
+// and the skip D) or one number per (token, head, row of S) (gated linear attention: c = 1, D = 0).  k and q may be
+// shared by the heads of a group (head h reads group h / (heads / groups)).  Everything inside the recurrence is
+// 32-bit; k, q and v are read in their own type (float32, or the compute dtype straight from a projection), q times
+// q_scale.
+//
+//   outer_recurrence_kernel<TI, NPT>   a CTA per (sequence, head, block of columns of S).  A column of S is cut over
+//       L lanes of one warp, lane l holding rows l, l + L, ... (NPT of them, in registers); tokens arrive in tiles
+//       through shared memory; per token every thread decays and updates its rows, multiplies them by q and the
+//       lanes' sums are added by shuffles.  Tokens are walked in order from the slot's state, so a result does not
+//       depend on how a prompt was cut.
+//   decay_softplus_kernel     dt = softplus(raw + bias), a = exp(-exp(A_log) dt) per (token, head), 32-bit.
+//   decay_lowrank_kernel      a = sigmoid(z)^(1 / tau) = exp(-softplus(-z) / tau), z = W2 r + b with r a short row per
+//                             token (the first of two projections, made with the mixer's other projections), 32-bit.
+//
+// ExiledOfCode/KuiperLLama has no recurrent mixer (its mixer is mha_kernel.cu:61,74-106).
+#include "common.cuh"
+
+namespace kl {
+
+constexpr int OR_THREADS = 128;
+constexpr int OR_TILE = 8;            // tokens per shared-memory tile
+
+struct OuterArgs {
+    const void* q; long long ld_q; int q_col;        // [rows, >= q_col + groups * N]
+    const void* k; long long ld_k; int k_col;
+    const void* v; long long ld_v; int v_col;        // [rows, >= v_col + heads * P]
+    const float* a; long long ld_a;                  // [rows, heads] or [rows, heads * N]
+    const float* c; long long ld_c;                  // [rows, heads] or null
+    const float* skip;                               // [heads] or null
+    float* state; long long ld_state;                // the slot's S at state + slot * ld_state, [heads, N, P]
+    float* y; long long ld_y;                        // [rows, heads * P]
+    const int* cu_tokens; const int* seq_slots;
+    int heads, groups, N, P, L, a_per_row;
+    float q_scale;
+};
+
+template <typename TI, int NPT>
+__global__ void __launch_bounds__(OR_THREADS)
+outer_recurrence_kernel(const OuterArgs A) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float sm[];
+    const int s = blockIdx.z, h = blockIdx.y;
+    const int row0 = A.cu_tokens[s], n_new = A.cu_tokens[s + 1] - row0;
+    if (n_new <= 0) return;
+    const int N = A.N, P = A.P, L = A.L;
+    const int cols_per_cta = OR_THREADS / L;
+    const int lane = threadIdx.x % L;
+    const int col = blockIdx.x * cols_per_cta + threadIdx.x / L;
+    const bool live = col < P;
+    const int g = h / (A.heads / A.groups);
+    // shared: per tile token: k [N] (times c), q [N] (times q_scale), a [N or 1], v [cols_per_cta]
+    const int a_len = A.a_per_row ? N : 1;
+    const int per_tok = 2 * N + a_len + cols_per_cta;
+    float* S_slot = A.state + (size_t)A.seq_slots[s] * A.ld_state + (size_t)h * N * P;
+    float S[NPT];
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+        const int n = i * L + lane;
+        S[i] = (live && n < N) ? S_slot[(size_t)n * P + col] : 0.f;
+    }
+    const TI* qp = (const TI*)A.q; const TI* kp = (const TI*)A.k; const TI* vp = (const TI*)A.v;
+    const float skip = A.skip != nullptr ? A.skip[h] : 0.f;
+    for (int t0 = 0; t0 < n_new; t0 += OR_TILE) {
+        const int nt = min(OR_TILE, n_new - t0);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nt * per_tok; idx += OR_THREADS) {
+            const int tt = idx / per_tok, j = idx - tt * per_tok;
+            const size_t row = (size_t)(row0 + t0 + tt);
+            float val;
+            if (j < N) {
+                val = to_f32(kp[row * A.ld_k + A.k_col + (size_t)g * N + j]);
+                if (A.c != nullptr) val *= A.c[row * A.ld_c + h];
+            } else if (j < 2 * N) {
+                val = to_f32(qp[row * A.ld_q + A.q_col + (size_t)g * N + (j - N)]) * A.q_scale;
+            } else if (j < 2 * N + a_len) {
+                val = A.a_per_row ? A.a[row * A.ld_a + (size_t)h * N + (j - 2 * N)] : A.a[row * A.ld_a + h];
+            } else {
+                const int cc = blockIdx.x * cols_per_cta + (j - 2 * N - a_len);
+                val = cc < P ? to_f32(vp[row * A.ld_v + A.v_col + (size_t)h * P + cc]) : 0.f;
+            }
+            sm[idx] = val;
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            const float* kk = sm + tt * per_tok;
+            const float* qq = kk + N;
+            const float* aa = qq + N;
+            const float vv = aa[a_len + threadIdx.x / L];
+            float acc = 0.f;
+            if (A.a_per_row) {
+#pragma unroll
+                for (int i = 0; i < NPT; ++i) {
+                    const int n = i * L + lane;
+                    if (n < N) {
+                        S[i] = fmaf(aa[n], S[i], kk[n] * vv);
+                        acc = fmaf(S[i], qq[n], acc);
+                    }
+                }
+            } else {
+                const float a0 = aa[0];
+#pragma unroll
+                for (int i = 0; i < NPT; ++i) {
+                    const int n = i * L + lane;
+                    if (n < N) {
+                        S[i] = fmaf(a0, S[i], kk[n] * vv);
+                        acc = fmaf(S[i], qq[n], acc);
+                    }
+                }
+            }
+            for (int o = L >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (lane == 0 && live) A.y[(size_t)(row0 + t0 + tt) * A.ld_y + (size_t)h * P + col] = fmaf(skip, vv, acc);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+        const int n = i * L + lane;
+        if (live && n < N) S_slot[(size_t)n * P + col] = S[i];
+    }
+}
+
+__global__ void decay_softplus_kernel(const void* __restrict__ raw, long long ld_raw, int col, int bf, const float* __restrict__ bias,
+                                      const float* __restrict__ A_log, int rows, int heads, float* __restrict__ dt,
+                                      float* __restrict__ a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= rows * heads) return;
+    const int t = idx / heads, h = idx - t * heads;
+    const size_t at = (size_t)t * ld_raw + col + h;
+    float z = (bf ? __bfloat162float(((const bf16*)raw)[at]) : ((const float*)raw)[at]) + bias[h];
+    const float d = z > 20.f ? z : log1pf(expf(z));
+    dt[idx] = d;
+    a[idx] = expf(-expf(A_log[h]) * d);
+}
+
+// a[t, c] = exp(-softplus(-z) / tau), z = b[c] + sum_r W2[c, r] * r1[t, r]
+template <typename T>
+__global__ void __launch_bounds__(256)
+decay_lowrank_kernel(const T* __restrict__ r1, long long ld_r1, int col, int rank, const float* __restrict__ W2,
+                     const float* __restrict__ b, float inv_tau, int rows, int channels, float* __restrict__ a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float row[];
+    const int t = blockIdx.x;
+    for (int r = threadIdx.x; r < rank; r += blockDim.x) row[r] = to_f32(r1[(size_t)t * ld_r1 + col + r]);
+    __syncthreads();
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
+        float z = 0.f;
+        for (int r = 0; r < rank; ++r) z = fmaf(W2[(size_t)c * rank + r], row[r], z);
+        z += b != nullptr ? b[c] : 0.f;
+        const float nz = -z;
+        const float sp = nz > 20.f ? nz : log1pf(expf(nz));
+        a[(size_t)t * channels + c] = expf(-sp * inv_tau);
+    }
+}
+
+}  // namespace kl
+
+using namespace kl;
+
+// in_dtype: the type of q, k and v (KL_F32 or KL_BF16).  a_per_row != 0: a is [rows, heads * N].
+KL_API int kl_outer_recurrence(const void* q, long long ld_q, int q_col, const void* k, long long ld_k, int k_col, const void* v,
+                               long long ld_v, int v_col, const float* a, long long ld_a, int a_per_row, const float* c,
+                               long long ld_c, const float* skip, float* state, long long ld_state, float* y, long long ld_y,
+                               const int* cu_tokens, const int* seq_slots, int n_seqs, int heads, int groups, int N, int P,
+                               float q_scale, int in_dtype, cudaStream_t stream) {
+    if (n_seqs <= 0) return KL_OK;
+    if (heads <= 0 || groups <= 0 || heads % groups || N <= 0 || P <= 0 || N > 1024) return KL_ERR_BAD_SIZE;
+    if (in_dtype != KL_F32 && in_dtype != KL_BF16) return KL_ERR_BAD_DTYPE;
+    // lanes per column: rows of S in registers per thread at most 16 where 32 lanes allow it
+    int L = 1;
+    while (L < 32 && (N + L - 1) / L > 16) L <<= 1;
+    const int npt = (N + L - 1) / L;
+    OuterArgs A;
+    A.q = q; A.ld_q = ld_q; A.q_col = q_col; A.k = k; A.ld_k = ld_k; A.k_col = k_col; A.v = v; A.ld_v = ld_v; A.v_col = v_col;
+    A.a = a; A.ld_a = ld_a; A.c = c; A.ld_c = ld_c; A.skip = skip; A.state = state; A.ld_state = ld_state; A.y = y; A.ld_y = ld_y;
+    A.cu_tokens = cu_tokens; A.seq_slots = seq_slots; A.heads = heads; A.groups = groups; A.N = N; A.P = P; A.L = L;
+    A.a_per_row = a_per_row ? 1 : 0; A.q_scale = q_scale;
+    const int cols = OR_THREADS / L;
+    dim3 grid((P + cols - 1) / cols, heads, n_seqs);
+    const size_t smem = (size_t)OR_TILE * (2 * N + (a_per_row ? N : 1) + cols) * sizeof(float);
+    if (smem > 200 * 1024) return KL_ERR_BAD_SIZE;
+#define KL_OR(TI, NPT)                                                                                              \
+    do {                                                                                                            \
+        if (smem > 48 * 1024)                                                                                       \
+            KL_CUDA(cudaFuncSetAttribute(outer_recurrence_kernel<TI, NPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        launch_kernel(outer_recurrence_kernel<TI, NPT>, grid, OR_THREADS, smem, stream, A);                         \
+    } while (0)
+#define KL_OR_BY_NPT(TI)                                                                                            \
+    do {                                                                                                            \
+        if (npt <= 4) KL_OR(TI, 4); else if (npt <= 8) KL_OR(TI, 8); else if (npt <= 16) KL_OR(TI, 16); else KL_OR(TI, 32); \
+    } while (0)
+    if (in_dtype == KL_F32) KL_OR_BY_NPT(float); else KL_OR_BY_NPT(bf16);
+#undef KL_OR_BY_NPT
+#undef KL_OR
+    KL_LAUNCH_CHECK();
+    return KL_OK;
+}
+
+KL_API int kl_decay_softplus(const void* raw, long long ld_raw, int col, int dtype, const float* bias, const float* A_log, int rows,
+                             int heads, float* dt, float* a, cudaStream_t stream) {
+    if (rows <= 0 || heads <= 0) return KL_OK;
+    if (dtype != KL_F32 && dtype != KL_BF16) return KL_ERR_BAD_DTYPE;
+    const int total = rows * heads;
+    launch_kernel(decay_softplus_kernel, (total + 255) / 256, 256, 0, stream, raw, ld_raw, col, (int)(dtype == KL_BF16), bias, A_log, rows,
+                  heads, dt, a);
+    KL_LAUNCH_CHECK();
+    return KL_OK;
+}
+
+KL_API int kl_decay_lowrank(const void* r1, long long ld_r1, int col, int rank, const float* W2, const float* b, float tau, int rows,
+                            int channels, float* a, int dtype, cudaStream_t stream) {
+    if (rows <= 0 || channels <= 0) return KL_OK;
+    if (rank <= 0 || rank > 4096 || !(tau > 0.f)) return KL_ERR_BAD_SIZE;
+    int yblocks = (channels + 255) / 256;
+    if (yblocks > 64) yblocks = 64;
+    dim3 grid(rows, yblocks);
+    if (dtype == KL_F32)
+        launch_kernel(decay_lowrank_kernel<float>, grid, 256, rank * sizeof(float), stream, (const float*)r1, ld_r1, col, rank, W2, b, 1.0f / tau,
+                      rows, channels, a);
+    else if (dtype == KL_BF16)
+        launch_kernel(decay_lowrank_kernel<bf16>, grid, 256, rank * sizeof(float), stream, (const bf16*)r1, ld_r1, col, rank, W2, b, 1.0f / tau,
+                      rows, channels, a);
+    else
+        return KL_ERR_BAD_DTYPE;
+    KL_LAUNCH_CHECK();
+    return KL_OK;
+}

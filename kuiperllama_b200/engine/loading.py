@@ -7,7 +7,7 @@ import torch
 
 from ..config import config_from_folder
 from ..parts.base import Runtime
-from ..weights.loader import load_tensors
+from ..weights.loader import load_tensors, tensor_shapes
 from ..weights.random_init import RandomTensors, write_random_model
 from .model import DecoderModel, ignorable_tensor_suffixes, model_manifest
 
@@ -35,6 +35,8 @@ def load_model(folder: str, dtype="bfloat16", device="cuda:0") -> DecoderModel:
     """The model that ``folder``'s config.json names, with the weights of its safetensors."""
     device = require_cuda(device)
     config = config_from_folder(folder)
+    if hasattr(config, "with_tensor_shapes"):          # sizes that a design leaves to its tensors' shapes
+        config = config.with_tensor_shapes(tensor_shapes(folder))
     spec = config.to_model_spec()
     tensors = load_tensors(folder, model_manifest(spec), ignorable=ignorable_tensor_suffixes(spec))
     model = DecoderModel(spec, tensors, Runtime(device=device, dtype=parse_dtype(dtype)))

@@ -98,7 +98,8 @@ class DecoderModel:
         storage (per-slot state of fixed size is not counted)."""
         kv, _, src = self.cache_requests()
         esize = torch.empty(0, dtype=self.runtime.dtype).element_size()
-        return sum((1 if r.kind == "keys" else 2) * r.kv_heads * r.head_dim * esize for r, s in zip(kv, src) if r is not None and s is None)
+        return sum(r.kv_heads * (r.head_dim + (0 if r.kind == "keys" else (r.value_dim or r.head_dim))) * esize
+                   for r, s in zip(kv, src) if r is not None and s is None)
 
     # ------------------------------------------------------------------ forward
     def hidden_states(self, step: StepContext, cache: SequenceCache) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:

@@ -125,6 +125,15 @@ class PostNormed:
     norm: Optional["Norm"] = None             # applied to the gated value; has weight, bias, eps, kind
 
 
+@dataclass
+class DeltaSum:
+    """Results of two sublayers that read the same stream and are added to it together: x += (first + second).  Each is
+    rows in the compute dtype or float32 pieces [S, n_tokens, hidden] (``second`` may be None).  The norm that reads the
+    stream next adds them in its own kernel (``ops.pair_rmsnorm``)."""
+    first: torch.Tensor
+    second: Optional[torch.Tensor] = None
+
+
 class Part:
     """Base of all parts."""
 

@@ -6,7 +6,7 @@ from typing import Optional, Tuple
 import torch
 
 from ..cache import CacheView
-from .base import FeedForward, Mixer, Norm, NormedLazy, PostNormed, ResidualGate, StepContext, StreamSink, register_arrangement
+from .base import DeltaSum, FeedForward, Mixer, Norm, NormedLazy, PostNormed, ResidualGate, StepContext, StreamSink, register_arrangement
 
 
 @register_arrangement("pre_norm")
@@ -89,3 +89,35 @@ class SandwichBlock:
         if isinstance(h, NormedLazy):
             h = h.dense()
         return residual, self._result(self.feed_forward.forward(h, step), h, self.feed_forward_gate, self.feed_forward_post_norm)
+
+
+@register_arrangement("parallel")
+class ParallelBlock:
+    """Both sublayers read the same stream and their results are added together:
+
+        x += (mixer(norm1(x)) + feed_forward(norm2(x)))          (x += mixer(norm1(x)) without a feed-forward)
+
+    The two RMS norms share their root mean square, so one kernel adds what the block before left
+    pending (32-bit), writes the stream and makes both normalised rows; the block's own two results
+    travel on as ``DeltaSum`` to the norm that reads the stream next.  Norms of other kinds run one
+    after the other.  KuiperLLama has the sequential pre-norm block alone
+    (kuiper/source/model/llama3.cpp:155-164)."""
+
+    def __init__(self, mixer_norm: Norm, mixer: Mixer, feed_forward_norm: Optional[Norm], feed_forward: Optional[FeedForward]):
+        self.mixer_norm, self.mixer = mixer_norm, mixer
+        self.feed_forward_norm, self.feed_forward = feed_forward_norm, feed_forward
+
+    def forward(self, residual: torch.Tensor, pending, step: StepContext, cache: CacheView):
+        step.residual_sink = None
+        a, b = self.mixer_norm, self.feed_forward_norm if self.feed_forward is not None else None
+        if b is not None and hasattr(a, "forward_pair") and type(a) is type(b) and a.eps == b.eps:
+            h1, h2 = a.forward_pair(residual, pending, b)
+        else:
+            h1 = a.forward(residual, pending, step.n_tokens)
+            if isinstance(h1, NormedLazy):
+                h1 = h1.dense()
+            h2 = b.forward(residual, None, step.n_tokens) if b is not None else None
+        mixed = self.mixer.forward(h1, step, cache)
+        if self.feed_forward is None:
+            return residual, mixed
+        return residual, DeltaSum(mixed, self.feed_forward.forward(h2, step))

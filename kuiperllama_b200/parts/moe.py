@@ -20,7 +20,10 @@ class MoEFeedForward(FeedForward):
         z = W_router n (32-bit);  s = softmax(z) over all experts;  the ``top`` largest s are chosen
         expert e:  g = min(W_gate[e] n, limit), u = clamp(W_up[e] n, -limit, limit),
                    f_e = W_down[e] (g * sigmoid(alpha * g) * (u + shift))          (no clamp when limit is None)
-        out = sum over the chosen e of s_e * f_e     (the weights are divided by their sum if ``renormalise``)
+        out = sum over the chosen e of s_e * f_e     (the weights are divided by their sum + ``renorm_eps`` if ``renormalise``)
+
+    With ``groups`` > 1 the experts form that many equal groups of neighbours; a group's score is the largest score in
+    it, and only experts of the ``keep_groups`` best groups can be chosen.
 
     Routing stays on the device (``ops.moe_route`` / ``moe_plan``): the (token, choice) pairs are sorted by
     expert into a list padded to whole tiles, one grouped product makes gate, up and the activation for
@@ -31,7 +34,7 @@ class MoEFeedForward(FeedForward):
     otherwise (float32, odd sizes).
 
     Spec: ``hidden_size``, ``experts``, ``top``, ``expert_size``, ``limit``, ``alpha``, ``shift``, ``renormalise``,
-    ``names``: router and, with ``{e}`` for the expert's number, gate, up, down.  KuiperLLama's only feed-forward is
+    ``renorm_eps``, ``groups``, ``keep_groups``, ``names``: router and, with ``{e}`` for the expert's number, gate, up, down.  KuiperLLama's only feed-forward is
     the dense SwiGLU (kuiper/source/model/llama3.cpp:692-718)."""
 
     # Mean rows per expert from which the list is cut into tiles of 128 for the tensor cores.  Measured at width 2,048 with 16
@@ -58,6 +61,10 @@ class MoEFeedForward(FeedForward):
         limit = spec.get("limit")
         self.activation = (float(limit) if limit is not None else 0.0, float(spec.get("alpha", 1.0)), float(spec.get("shift", 0.0)))
         self.renormalise = bool(spec.get("renormalise", False))
+        self.renorm_eps = float(spec.get("renorm_eps", 0.0))
+        self.groups, self.keep_groups = int(spec.get("groups", 1)), int(spec.get("keep_groups", 1))
+        if self.E % self.groups or not 1 <= self.keep_groups <= self.groups or self.top > self.keep_groups * (self.E // self.groups):
+            raise ValueError(f"{self.E} experts in {self.groups} groups of which {self.keep_groups} are kept do not hold {self.top} choices")
         n = spec["names"]
         dev, dt = runtime.device, runtime.dtype
         get = lambda key, e: tensors[prefix + n[key].format(e=e)].to(device=dev, dtype=dt)
@@ -74,7 +81,7 @@ class MoEFeedForward(FeedForward):
             x = x.dense()
         n, dev, dt = step.n_tokens, x.device, self.runtime.dtype
         logits = self.router.forward(x, out_dtype=torch.float32)
-        choice, weight = ops.moe_route(logits, self.top, self.renormalise)
+        choice, weight = ops.moe_route(logits, self.top, self.renormalise, self.groups, self.keep_groups, self.renorm_eps)
         if self.tensor_cores and n * self.top >= self.TENSOR_CORE_ROWS_PER_EXPERT * self.E and x.stride(0) % 8 == 0:
             # enough rows per expert to fill tiles of 128: both products on the tensor cores, the activation in the first one's epilogue
             pair_pos, list_rows, tile_group = ops.moe_plan(choice, self.E, 128, step.token_slot)

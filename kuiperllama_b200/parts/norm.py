@@ -8,7 +8,7 @@ import torch
 from ..config.spec import PartSpec
 from ..csrc import ops
 from ..weights.loader import TensorDecl
-from .base import Accumulated, Norm, NormedLazy, PostNormed, Runtime, register_norm
+from .base import Accumulated, DeltaSum, Norm, NormedLazy, PostNormed, Runtime, register_norm
 
 
 @register_norm("rmsnorm")
@@ -36,6 +36,8 @@ class RMSNorm(Norm):
     def forward(self, residual: torch.Tensor, delta, n_rows: int, rows: Optional[torch.Tensor] = None):
         if isinstance(delta, PostNormed):
             return chain_forward(self, residual, delta, rows)
+        if isinstance(delta, DeltaSum):
+            return self.forward_pair(residual, delta, None, rows)[0]
         if isinstance(delta, Accumulated):
             # the stream holds the sum already; if the rows times this norm's weight came with it,
             # the product that follows only has to apply 1 / rms
@@ -46,6 +48,21 @@ class RMSNorm(Norm):
         out = torch.empty((n_out, self.size), dtype=self.runtime.dtype, device=residual.device)
         ops.add_rmsnorm(residual, delta, self.weight, out, self.eps, rows)
         return out
+
+
+def _forward_pair(self, residual: torch.Tensor, delta, other: Optional["RMSNorm"], rows: Optional[torch.Tensor] = None):
+    """This norm and ``other`` (a second RMS norm with the same eps, or None) of the same stream after ``delta`` (None, a
+    tensor, pieces or ``DeltaSum``) has been added: one kernel, one root mean square, two weights."""
+    parts = (delta.first, delta.second) if isinstance(delta, DeltaSum) else (delta,)
+    n_out = rows.numel() if rows is not None else residual.shape[0]
+    dt, dev = self.runtime.dtype, residual.device
+    out1 = torch.empty((n_out, self.size), dtype=dt, device=dev)
+    out2 = torch.empty((n_out, self.size), dtype=dt, device=dev) if other is not None else None
+    ops.pair_rmsnorm(residual, parts, self.weight, other.weight if other is not None else None, out1, out2, self.eps, rows, dtype=dt)
+    return out1, out2
+
+
+RMSNorm.forward_pair = _forward_pair
 
 
 def chain_forward(norm: Norm, residual: torch.Tensor, delta, rows: Optional[torch.Tensor]) -> torch.Tensor:
@@ -69,6 +86,10 @@ def add_to_stream(residual: torch.Tensor, delta) -> None:
     """Add a pending delta to the stream without a norm after it (what a caller that wants the
     stream itself does after the last block)."""
     if delta is None:
+        return
+    if isinstance(delta, DeltaSum):
+        ops.pair_rmsnorm(residual, (delta.first, delta.second), None, None, None, None, 0.0,
+                         dtype=next((d.dtype for d in (delta.first, delta.second) if d is not None and d.dim() == 2), torch.float32))
         return
     if isinstance(delta, PostNormed):
         post = None

@@ -1,6 +1,6 @@
 """Weights: safetensors by tensor name, and random model folders."""
-from .loader import TensorDecl, WeightsError, load_tensors, stored_dtype
+from .loader import TensorDecl, WeightsError, load_tensors, stored_dtype, tensor_shapes
 from .safetensors_io import SafetensorsFile, SafetensorsFormatError, write_safetensors
 
-__all__ = ["TensorDecl", "WeightsError", "load_tensors", "stored_dtype", "SafetensorsFile",
+__all__ = ["TensorDecl", "WeightsError", "load_tensors", "stored_dtype", "tensor_shapes", "SafetensorsFile",
            "SafetensorsFormatError", "write_safetensors"]

@@ -93,6 +93,11 @@ def stored_dtype(file_dtype: torch.dtype, role: str) -> Optional[torch.dtype]:
     return torch.float32
 
 
+def tensor_shapes(folder: str) -> Dict[str, Tuple[int, ...]]:
+    """Name -> shape of every tensor of the folder's checkpoint, from the headers alone."""
+    return {name: tuple(sf.entries[name].shape) for name, (sf, _) in _open_files(folder).items()}
+
+
 def load_tensors(folder: str, manifest: Dict[str, TensorDecl],
                  ignorable: Iterable[str] = ()) -> Dict[str, torch.Tensor]:
     """All tensors of ``manifest`` as CPU tensors.  Names in the checkpoint that the
