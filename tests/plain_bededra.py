@@ -82,32 +82,42 @@ def visible(i: int, j: int, size: int, keep_first: int) -> bool:
     return j <= i and (i - j < size or j < keep_first)
 
 
-def mixed_head_attention(h: torch.Tensor, W: Dict[str, torch.Tensor], m: dict) -> torch.Tensor:
-    """Softmax attention without rotation: soft-capped scores less a distance bias, a sliding window that also keeps the
-    first tokens, the heads' weights mixed after the softmax, a gate per head.  W: q, k, v, r1, r2, talk, g, o."""
-    T = h.shape[0]
-    H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    size, keep = m["mask"]["size"], m["mask"]["keep_first"]
-    cap, scale = float(m["softcap"]), float(m["scale"])
-    q = (h @ W["q"].T).reshape(T, H, d)
-    k = (h @ W["k"].T).reshape(T, G, d)
-    v = (h @ W["v"].T).reshape(T, G, dv)
-    per = H // G
+def mixed_attention_weights(q: torch.Tensor, k: torch.Tensor, m: dict, r1, r2, talk):
+    """q [T, H, d], k [T, G, d] -> (softmax weights [H, T, T], the weights after the heads were mixed [H, T, T])."""
+    T, H = q.shape[0], q.shape[1]
+    per = H // k.shape[1]
+    mask_cfg = m.get("mask")
+    size, keep = (mask_cfg["size"], mask_cfg.get("keep_first", 0)) if mask_cfg else (T + 1, 0)
+    cap, scale = m.get("softcap"), float(m["scale"])
     idx = torch.arange(T)
     dist = (idx[:, None] - idx[None, :]).clamp(min=0).to(F)                  # i - j
     mask = torch.tensor([[visible(i, j, size, keep) for j in range(T)] for i in range(T)])
     weights = torch.zeros(H, T, T, dtype=F)
     for hh in range(H):
         s = (q[:, hh] @ k[:, hh // per].T) * scale
-        s = cap * torch.tanh(s / cap)
-        s = s - W["r1"][hh] * torch.log1p(W["r2"][hh] * dist)
+        if cap is not None:
+            s = float(cap) * torch.tanh(s / float(cap))
+        if r1 is not None:
+            s = s - r1[hh] * torch.log1p(r2[hh] * dist)
         s = s.masked_fill(~mask, -math.inf)
         weights[hh] = torch.softmax(s, dim=-1)
-    mixed = torch.einsum("hg,gij->hij", W["talk"], weights)
+    mixed = weights if talk is None else torch.einsum("hg,gij->hij", talk, weights)
+    return weights, mixed
+
+
+def mixed_head_attention(h: torch.Tensor, W: Dict[str, torch.Tensor], m: dict) -> torch.Tensor:
+    """Softmax attention without rotation: soft-capped scores less a distance bias, a sliding window that also keeps the
+    first tokens, the heads' weights mixed after the softmax, a gate per head.  W: q, k, v, r1, r2, talk, g, o."""
+    T = h.shape[0]
+    H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    q = (h @ W["q"].T).reshape(T, H, d)
+    k = (h @ W["k"].T).reshape(T, G, d)
+    v = (h @ W["v"].T).reshape(T, G, dv)
+    _, mixed = mixed_attention_weights(q, k, m, W.get("r1"), W.get("r2"), W.get("talk"))
     gate = torch.sigmoid(h @ W["g"].T)                                       # [T, H]
     out = torch.zeros(T, H, dv, dtype=F)
     for hh in range(H):
-        out[:, hh] = (mixed[hh] @ v[:, hh // per]) * gate[:, hh:hh + 1]
+        out[:, hh] = (mixed[hh] @ v[:, hh // (H // G)]) * gate[:, hh:hh + 1]
     return out.reshape(T, H * dv) @ W["o"].T
 
 
