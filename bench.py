@@ -4,7 +4,7 @@ B200, and the two other workloads of the same family (Llama-2-7B shape with ragg
 Llama-3.2-1B shape with temperature sampling).
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B] [--impl reference] [--no-points]
-    python bench.py --compare terolix|munadra [--sizes 1b,8b-8-layers]      (another design beside Llama; see compare_designs)
+    python bench.py --compare terolix|munadra|bededra [--sizes 1b,8b-8-layers]      (another design beside Llama; see compare_designs)
 
 A "step" is one decode step of a batch (default 8 sequences that each hold a 512-token
 prompt, context limit 4096).  One JSON line is printed:
@@ -393,6 +393,24 @@ def munadra_config(width, layers, heads, head_dim, vocab):
             "logit_scale": 1.0, "logit_softcap": 30.0, "layers": out}
 
 
+def bededra_config(width, layers, heads, kv_heads, head_dim, vocab):
+    """A Bededra model of ``layers`` layers in groups of four: a state-space layer (inner size twice the width, heads of 64,
+    a state of 128 rows, a dense feed-forward of squared relu as large as the Llama shape's three matrices), two layers of
+    windowed softmax attention (the Llama shape's heads; a window of 1,024 with 64 kept first tokens) beside gated linear
+    attention (keys half the width, values the width, heads of 64 and 128), and a state-space layer; the last three with 16
+    experts in 4 groups of which 2 are kept, 4 experts per token of a quarter of the Llama shape's intermediate size each."""
+    inter = COMPARE_INTER[width]
+    ssm = {"type": "mamba2", "mixer": {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}}
+    par = {"type": "parallel", "mixer": {
+        "left": {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5, "softcap": 50.0,
+                 "mask": {"size": 1024, "keep_first": 64}},
+        "right": {"heads": width // 128, "dim": 64, "vdim": 128, "tau": 16.0, "rank": 16}, "left_scale": 1.0, "right_scale": 1.0}}
+    moe = {"kind": "moe", "router": {"experts": 16, "top": 4, "groups": {"count": 4, "keep": 2}}, "expert": {"ff": inter // 4}}
+    order = [dict(ssm, mlp={"kind": "dense", "ff": 3 * inter // 2}), dict(par, mlp=moe), dict(par, mlp=moe), dict(ssm, mlp=moe)]
+    return {"architecture": "Bededra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "canon": {"taps": 4},
+            "layers": [order[i % 4] for i in range(layers)]}
+
+
 COMPARE_INTER = {2048: 8192, 4096: 14336}
 
 
@@ -406,7 +424,7 @@ COMPARE_SIZES = {
 
 
 def compare_designs(args):
-    """``--compare terolix`` (or ``munadra``): prefill (one prompt of 2,048 tokens) and decode (8 and 64 sequences after
+    """``--compare terolix`` (or ``munadra``, ``bededra``): prefill (one prompt of 2,048 tokens) and decode (8 and 64 sequences after
     512-token prompts, CUDA graphs) of Terolix beside the Llama decoder at equal size, random weights,
     bfloat16.  Rates in tokens a second; ``hbm_frac`` is the weights' bytes over the decode step's time
     over the copy peak, ``tc_frac`` the prefill's matrix-product flops over its time over the bf16 peak."""
@@ -426,6 +444,8 @@ def compare_designs(args):
                      tie_word_embeddings=True)
         if args.compare == "munadra":
             other = munadra_config(z["width"], z["layers"], z["heads"], z["head_dim"], vocab)
+        elif args.compare == "bededra":
+            other = bededra_config(z["width"], z["layers"], z["heads"], z["kv_heads"], z["head_dim"], vocab)
         else:
             other = terolix_config(z["width"], z["layers"], z["heads"], z["kv_heads"], z["head_dim"], z["ff"], vocab)
         out[name] = {}
@@ -434,8 +454,8 @@ def compare_designs(args):
             infer = kl.Inference(model, max_tokens=64 * CONTEXT, max_batch=64, max_seq_len=CONTEXT)
             wbytes = model.weight_bytes()
             matrix_params = wbytes / 2 - vocab * z["width"]
-            if design == "munadra":          # a token uses 4 of a layer's 16 experts: count what it multiplies by
-                moe_layers = sum(1 for l in cfg["layers"] if l["mlp"]["kind"] == "moe")
+            if design in ("munadra", "bededra"):          # a token uses 4 of a layer's 16 experts: count what it multiplies by
+                moe_layers = sum(1 for l in cfg["layers"] if l["mlp"] and l["mlp"]["kind"] == "moe")
                 matrix_params -= moe_layers * 12 * 3 * z["width"] * (COMPARE_INTER[z["width"]] // 4)
             t = time_prefill(infer, warmup=3, repeats=5, seed=2, checks=checks)
             r = {"weight_gb": round(wbytes / 1e9, 3), "prefill_tokens_per_s": round(PREFILL_LEN / t, 1), "prefill_ms": round(t * 1e3, 3),
@@ -484,7 +504,7 @@ def main():
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--no-points", action="store_true",
                     help="only the headline: skip the prefill, the batch 1, 64 and 128 points and the two other workloads")
-    ap.add_argument("--compare", default=None, choices=["terolix", "munadra"],
+    ap.add_argument("--compare", default=None, choices=["terolix", "munadra", "bededra"],
                     help="instead of the default workload: this design beside Llama at equal size (prefill and decode rates)")
     ap.add_argument("--sizes", default="", help="with --compare: which of the sizes to run, with commas (default: all)")
     args = ap.parse_args()
