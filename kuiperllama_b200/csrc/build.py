@@ -45,6 +45,7 @@ SOURCES: Dict[str, str] = {
     "short_conv": "short_conv.cu",
     "outer_recurrence": "outer_recurrence.cu",
     "attention_mixed": "attention_mixed.cu",
+    "attention_mixed_tiled": "attention_mixed_tiled.cu",
 }
 HEADERS: List[str] = ["common.cuh", "tcgen05.cuh", "tma_host.cuh", "attention_decode_noalloc.h"]
 

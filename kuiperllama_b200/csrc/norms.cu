@@ -283,6 +283,44 @@ head_rmsnorm_gate_kernel(const float* __restrict__ x, const T* __restrict__ gate
     }
 }
 
+// The same for long rows (a norm over hundreds of channels or more): one CTA per (token, head).
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_rmsnorm_gate_block_kernel(const float* __restrict__ x, const T* __restrict__ gate, long long gate_ld, const float* __restrict__ w,
+                               T* __restrict__ out, long long out_ld, float out_scale, int heads, int dim, float eps, int gate_first,
+                               int wide_weight) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const int t = blockIdx.x / heads, h = blockIdx.x - t * heads;
+    const float* xr = x + ((size_t)t * heads + h) * dim;
+    const T* g = gate ? gate + (size_t)t * gate_ld + (size_t)h * dim : nullptr;
+    const float* wr = w != nullptr ? w + (wide_weight ? (size_t)h * dim : 0) : nullptr;
+    T* o = out + (size_t)t * out_ld + (size_t)h * dim;
+    const bool first = gate_first && g != nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        float y = xr[i];
+        if (first) { const float a = to_f32(g[i]); y *= a / (1.0f + expf(-a)); }
+        ss += y * y;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        float y = xr[i];
+        if (first) {
+            const float a = to_f32(g[i]);
+            y = y * (a / (1.0f + expf(-a))) * inv;
+            if (wr != nullptr) y *= wr[i];
+        } else {
+            y *= inv;
+            if (wr != nullptr) y *= wr[i];
+            if (g != nullptr) { const float a = to_f32(g[i]); y *= a / (1.0f + expf(-a)); }
+        }
+        o[i] = from_f32<T>(y * out_scale);
+    }
+}
+
 // The norms of a block whose two sublayers read the same stream: x = residual + (d1 + d2) (each delta rows in the
 // compute dtype or float32 pieces, or absent), written back; one root mean square; out1 = x / rms * w1 and
 // out2 = x / rms * w2 (out2 optional).  With `rows` only those rows are read, into out1[0..), and the stream stays.
@@ -310,8 +348,10 @@ pair_rmsnorm_kernel(float* __restrict__ residual, const PairDelta d1, const Pair
         if (has) {
             float add = 0.f;
             if (d1.rows != nullptr) add += to_f32(((const T*)d1.rows)[row * d1.ld + i]);
+#pragma unroll 4
             for (int p = 0; p < d1.n_pieces; ++p) add += d1.pieces[(size_t)p * d1.piece_stride + row * hidden + i];
             if (d2.rows != nullptr) add += to_f32(((const T*)d2.rows)[row * d2.ld + i]);
+#pragma unroll 4
             for (int p = 0; p < d2.n_pieces; ++p) add += d2.pieces[(size_t)p * d2.piece_stride + row * hidden + i];
             v += add;
             if (rows == nullptr) x[i] = v;
@@ -395,6 +435,16 @@ KL_API int kl_head_rmsnorm_gate(const float* x, const void* gate, long long gate
     if (tokens <= 0 || heads <= 0) return KL_OK;
     if (dim <= 0) return KL_ERR_BAD_SIZE;
     const long long items = (long long)tokens * heads;
+    if (dim >= 512) {
+        if (dtype == KL_F32)
+            launch_kernel(head_rmsnorm_gate_block_kernel<float>, (int)items, 256, 0, stream, x, (const float*)gate, gate_ld, w, (float*)out, out_ld, out_scale, heads, dim, eps, gate_first, wide_weight);
+        else if (dtype == KL_BF16)
+            launch_kernel(head_rmsnorm_gate_block_kernel<bf16>, (int)items, 256, 0, stream, x, (const bf16*)gate, gate_ld, w, (bf16*)out, out_ld, out_scale, heads, dim, eps, gate_first, wide_weight);
+        else
+            return KL_ERR_BAD_DTYPE;
+        KL_LAUNCH_CHECK();
+        return KL_OK;
+    }
     const int blocks = (int)((items + 3) / 4);
     if (dtype == KL_F32)
         launch_kernel(head_rmsnorm_gate_kernel<float>, blocks, 128, 0, stream, x, (const float*)gate, gate_ld, w, (float*)out, out_ld, out_scale, tokens, heads, dim, eps, gate_first, wide_weight);

@@ -837,6 +837,17 @@ def kv_append(src: torch.Tensor, k_col: int, v_col: int, k_cache: torch.Tensor, 
                                                kv_heads, dim, vdim, dtype_code(src.dtype), _stream()), "kv_append")
 
 
+def mixed_attention_splits(n_seqs: int, context_class: int, window: int, keep_first: int) -> int:
+    """Into how many pieces a decode step cuts each sequence's visible keys for the mixed-head attention: chunks of 32
+    keys dealt to the pieces in turn, about one CTA per SM over all sequences, at most one piece per chunk and 32.  Planned
+    from the engine's class of the longest sequence (16 pages, then one class per doubling), so a captured step stays valid."""
+    chunks = (16 << max(0, int(context_class))) * (PAGE // 32)
+    if window:
+        chunks = min(chunks, (int(window) + 31) // 32 + 1 + (int(keep_first or 0) + 31) // 32)
+    want = -(-sm_count() // max(1, int(n_seqs)))
+    return max(1, min(chunks, want, 32))
+
+
 def attention_mixed(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     block_table: torch.Tensor, step, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, softcap: float = 0.0,
                     r1: Optional[torch.Tensor] = None, r2: Optional[torch.Tensor] = None, talk: Optional[torch.Tensor] = None,
@@ -858,6 +869,20 @@ def attention_mixed(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Te
         _need(t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == count), "attention_mixed: float32 per-head tensors")
     _need((r1 is None) == (r2 is None), "attention_mixed: the distance bias needs both of its numbers")
     _need(heads % kv_heads == 0, "attention_mixed: heads must be a multiple of kv heads")
+    L = lib("attention_mixed_tiled")
+    max_new = int(step.max_new)
+    if L.kl_attention_mixed_tiled_fits(heads, kv_heads, dim, vdim, dtype_code(q.dtype), int(talk is not None), max_new):
+        splits = mixed_attention_splits(step.n_seqs, getattr(step, "context_class", 0), window, keep_first) if max_new == 1 else 1
+        ml = torch.empty((n, heads, splits, 2), dtype=torch.float32, device=q.device)
+        part = torch.empty((n, splits, heads * vdim), dtype=torch.float32, device=q.device) if splits > 1 else None
+        _check(L.kl_attention_mixed_tiled(
+            _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(gate), ctypes.c_longlong(gate.stride(0) if gate is not None else 0), _ptr(out),
+            ctypes.c_longlong(out.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(step.cu_tokens),
+            _ptr(step.seq_slots), _ptr(step.seq_starts), _ptr(step.token_slot), n, step.n_seqs, max_new, heads, kv_heads, dim, vdim,
+            ctypes.c_float(scale), ctypes.c_float(softcap or 0.0), _ptr(r1), _ptr(r2), _ptr(talk), int(window or 0), int(keep_first or 0),
+            ctypes.c_float(out_scale), splits, _ptr(ml), _ptr(part), dtype_code(q.dtype), _stream()), "attention_mixed_tiled",
+            3 if splits > 1 else 2)
+        return
     _check(lib("attention_mixed").kl_attention_mixed(
         _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(gate), ctypes.c_longlong(gate.stride(0) if gate is not None else 0), _ptr(out),
         ctypes.c_longlong(out.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(step.positions),
@@ -937,7 +962,8 @@ def device_words(device: torch.device) -> torch.Tensor:
     outside the vocabulary.  ``check_device_words`` reads both with one copy."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
     if idx not in _device_words:
-        _device_words[idx] = torch.zeros(2, dtype=torch.int32, device=device)
+        with torch.inference_mode(False):   # an ordinary tensor also when first asked for under inference mode: it is cleared in place later
+            _device_words[idx] = torch.zeros(2, dtype=torch.int32, device=device)
     return _device_words[idx]
 
 

@@ -23,8 +23,8 @@
 
 namespace kl {
 
-constexpr int OR_THREADS = 128;
-constexpr int OR_TILE = 8;            // tokens per shared-memory tile
+constexpr int OR_THREADS = 512;          // the most threads of a CTA; a launch takes 128, 256 or 512
+constexpr int OR_TILE = 16;           // tokens per shared-memory tile
 
 struct OuterArgs {
     const void* q; long long ld_q; int q_col;        // [rows, >= q_col + groups * N]
@@ -41,7 +41,7 @@ struct OuterArgs {
 };
 
 template <typename TI, int NPT>
-__global__ void __launch_bounds__(OR_THREADS)
+__global__ void __launch_bounds__(OR_THREADS, 1)
 outer_recurrence_kernel(const OuterArgs A) {
     pdl_launch_dependents();
     pdl_wait();
@@ -50,7 +50,8 @@ outer_recurrence_kernel(const OuterArgs A) {
     const int row0 = A.cu_tokens[s], n_new = A.cu_tokens[s + 1] - row0;
     if (n_new <= 0) return;
     const int N = A.N, P = A.P, L = A.L;
-    const int cols_per_cta = OR_THREADS / L;
+    const int threads = blockDim.x;
+    const int cols_per_cta = threads / L;
     const int lane = threadIdx.x % L;
     const int col = blockIdx.x * cols_per_cta + threadIdx.x / L;
     const bool live = col < P;
@@ -70,22 +71,33 @@ outer_recurrence_kernel(const OuterArgs A) {
     for (int t0 = 0; t0 < n_new; t0 += OR_TILE) {
         const int nt = min(OR_TILE, n_new - t0);
         __syncthreads();
-        for (int idx = threadIdx.x; idx < nt * per_tok; idx += OR_THREADS) {
-            const int tt = idx / per_tok, j = idx - tt * per_tok;
+        // the tile's k (times c), q (times q_scale), a and v, each in a loop of its own so that the loads of several
+        // turns are in flight together
+#pragma unroll 4
+        for (int idx = threadIdx.x; idx < nt * N; idx += threads) {
+            const int tt = idx / N, j = idx - tt * N;
             const size_t row = (size_t)(row0 + t0 + tt);
-            float val;
-            if (j < N) {
-                val = to_f32(kp[row * A.ld_k + A.k_col + (size_t)g * N + j]);
-                if (A.c != nullptr) val *= A.c[row * A.ld_c + h];
-            } else if (j < 2 * N) {
-                val = to_f32(qp[row * A.ld_q + A.q_col + (size_t)g * N + (j - N)]) * A.q_scale;
-            } else if (j < 2 * N + a_len) {
-                val = A.a_per_row ? A.a[row * A.ld_a + (size_t)h * N + (j - 2 * N)] : A.a[row * A.ld_a + h];
-            } else {
-                const int cc = blockIdx.x * cols_per_cta + (j - 2 * N - a_len);
-                val = cc < P ? to_f32(vp[row * A.ld_v + A.v_col + (size_t)h * P + cc]) : 0.f;
-            }
-            sm[idx] = val;
+            float val = to_f32(kp[row * A.ld_k + A.k_col + (size_t)g * N + j]);
+            if (A.c != nullptr) val *= A.c[row * A.ld_c + h];
+            sm[tt * per_tok + j] = val;
+        }
+#pragma unroll 4
+        for (int idx = threadIdx.x; idx < nt * N; idx += threads) {
+            const int tt = idx / N, j = idx - tt * N;
+            const size_t row = (size_t)(row0 + t0 + tt);
+            sm[tt * per_tok + N + j] = to_f32(qp[row * A.ld_q + A.q_col + (size_t)g * N + j]) * A.q_scale;
+        }
+#pragma unroll 4
+        for (int idx = threadIdx.x; idx < nt * a_len; idx += threads) {
+            const int tt = idx / a_len, j = idx - tt * a_len;
+            const size_t row = (size_t)(row0 + t0 + tt);
+            sm[tt * per_tok + 2 * N + j] = A.a_per_row ? A.a[row * A.ld_a + (size_t)h * N + j] : A.a[row * A.ld_a + h];
+        }
+        for (int idx = threadIdx.x; idx < nt * cols_per_cta; idx += threads) {
+            const int tt = idx / cols_per_cta, j = idx - tt * cols_per_cta;
+            const size_t row = (size_t)(row0 + t0 + tt);
+            const int cc = blockIdx.x * cols_per_cta + j;
+            sm[tt * per_tok + 2 * N + a_len + j] = cc < P ? to_f32(vp[row * A.ld_v + A.v_col + (size_t)h * P + cc]) : 0.f;
         }
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
@@ -122,6 +134,104 @@ outer_recurrence_kernel(const OuterArgs A) {
     for (int i = 0; i < NPT; ++i) {
         const int n = i * L + lane;
         if (live && n < N) S_slot[(size_t)n * P + col] = S[i];
+    }
+}
+
+// The same recurrence with R rows x C columns of S in a thread's registers: per token a thread reads R values each of
+// k, q (and a) and C of v for 3 R C multiply-adds, and only the column sums cross lanes.  A warp holds LR = 32 / CGW lanes
+// along the rows (lane = column group + CGW * row group; row n = row group + LR * i), so neighbouring lanes hold
+// neighbouring columns of a row.  Rows from N to LR * R are zero in shared memory and change nothing.
+template <typename TI, int R, int C>
+__global__ void __launch_bounds__(256)
+outer_recurrence_slab_kernel(const OuterArgs A) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float sm[];
+    const int s = blockIdx.z, h = blockIdx.y;
+    const int row0 = A.cu_tokens[s], n_new = A.cu_tokens[s + 1] - row0;
+    if (n_new <= 0) return;
+    const int N = A.N, P = A.P, LR = A.L, Np = LR * R;
+    const int threads = blockDim.x;
+    const int cgw = 32 / LR;                                   // column groups per warp
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int rg = lane / cgw, cg = warp * cgw + lane % cgw;   // the thread's row group, and its column group in the CTA
+    const int cols_per_cta = (threads / LR) * C;
+    const int col0 = blockIdx.x * cols_per_cta + cg * C;
+    const bool live = col0 < P;                                // P is a multiple of C
+    const int g = h / (A.heads / A.groups);
+    const int a_len = A.a_per_row ? Np : 1;
+    const int per_tok = 2 * Np + a_len + cols_per_cta;         // k (times c), q (times q_scale), a, v
+    float* S_slot = A.state + (size_t)A.seq_slots[s] * A.ld_state + (size_t)h * N * P;
+    float S[R][C];
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+        const int n = rg + LR * i;
+#pragma unroll
+        for (int j = 0; j < C; ++j) S[i][j] = (live && n < N) ? S_slot[(size_t)n * P + col0 + j] : 0.f;
+    }
+    const TI* qp = (const TI*)A.q; const TI* kp = (const TI*)A.k; const TI* vp = (const TI*)A.v;
+    const float skip = A.skip != nullptr ? A.skip[h] : 0.f;
+    for (int t0 = 0; t0 < n_new; t0 += OR_TILE) {
+        const int nt = min(OR_TILE, n_new - t0);
+        __syncthreads();
+#pragma unroll 4
+        for (int idx = threadIdx.x; idx < nt * Np; idx += threads) {
+            const int tt = idx / Np, j = idx - tt * Np;
+            const size_t row = (size_t)(row0 + t0 + tt);
+            float kv = 0.f, qv = 0.f;
+            if (j < N) {
+                kv = to_f32(kp[row * A.ld_k + A.k_col + (size_t)g * N + j]);
+                if (A.c != nullptr) kv *= A.c[row * A.ld_c + h];
+                qv = to_f32(qp[row * A.ld_q + A.q_col + (size_t)g * N + j]) * A.q_scale;
+            }
+            sm[tt * per_tok + j] = kv;
+            sm[tt * per_tok + Np + j] = qv;
+            if (A.a_per_row) sm[tt * per_tok + 2 * Np + j] = j < N ? A.a[row * A.ld_a + (size_t)h * N + j] : 0.f;
+        }
+        for (int idx = threadIdx.x; idx < nt * cols_per_cta; idx += threads) {
+            const int tt = idx / cols_per_cta, j = idx - tt * cols_per_cta;
+            const size_t row = (size_t)(row0 + t0 + tt);
+            const int cc = blockIdx.x * cols_per_cta + j;
+            sm[tt * per_tok + 2 * Np + a_len + j] = cc < P ? to_f32(vp[row * A.ld_v + A.v_col + (size_t)h * P + cc]) : 0.f;
+        }
+        if (!A.a_per_row)
+            for (int tt = threadIdx.x; tt < nt; tt += threads) sm[tt * per_tok + 2 * Np] = A.a[(size_t)(row0 + t0 + tt) * A.ld_a + h];
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            const float* kk = sm + tt * per_tok;
+            const float* qq = kk + Np;
+            const float* aa = qq + Np;
+            float v[C], acc[C];
+#pragma unroll
+            for (int j = 0; j < C; ++j) { v[j] = aa[a_len + cg * C + j]; acc[j] = 0.f; }
+            const float a0 = aa[0];
+#pragma unroll
+            for (int i = 0; i < R; ++i) {
+                const int n = rg + LR * i;
+                const float kn = kk[n], qn = qq[n], an = A.a_per_row ? aa[n] : a0;
+#pragma unroll
+                for (int j = 0; j < C; ++j) {
+                    S[i][j] = fmaf(an, S[i][j], kn * v[j]);
+                    acc[j] = fmaf(S[i][j], qn, acc[j]);
+                }
+            }
+            for (int o = cgw; o < 32; o <<= 1) {
+#pragma unroll
+                for (int j = 0; j < C; ++j) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+            }
+            if (rg == 0 && live) {
+                float* y = A.y + (size_t)(row0 + t0 + tt) * A.ld_y + (size_t)h * P + col0;
+#pragma unroll
+                for (int j = 0; j < C; ++j) y[j] = fmaf(skip, v[j], acc[j]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+        const int n = rg + LR * i;
+#pragma unroll
+        for (int j = 0; j < C; ++j)
+            if (live && n < N) S_slot[(size_t)n * P + col0 + j] = S[i][j];
     }
 }
 
@@ -174,16 +284,69 @@ KL_API int kl_outer_recurrence(const void* q, long long ld_q, int q_col, const v
     if (n_seqs <= 0) return KL_OK;
     if (heads <= 0 || groups <= 0 || heads % groups || N <= 0 || P <= 0 || N > 1024) return KL_ERR_BAD_SIZE;
     if (in_dtype != KL_F32 && in_dtype != KL_BF16) return KL_ERR_BAD_DTYPE;
-    // lanes per column: rows of S in registers per thread at most 16 where 32 lanes allow it
-    int L = 1;
-    while (L < 32 && (N + L - 1) / L > 16) L <<= 1;
-    const int npt = (N + L - 1) / L;
+    int sms = 0, dev = 0;
+    KL_CUDA(cudaGetDevice(&dev));
+    KL_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     OuterArgs A;
     A.q = q; A.ld_q = ld_q; A.q_col = q_col; A.k = k; A.ld_k = ld_k; A.k_col = k_col; A.v = v; A.ld_v = ld_v; A.v_col = v_col;
     A.a = a; A.ld_a = ld_a; A.c = c; A.ld_c = ld_c; A.skip = skip; A.state = state; A.ld_state = ld_state; A.y = y; A.ld_y = ld_y;
-    A.cu_tokens = cu_tokens; A.seq_slots = seq_slots; A.heads = heads; A.groups = groups; A.N = N; A.P = P; A.L = L;
+    A.cu_tokens = cu_tokens; A.seq_slots = seq_slots; A.heads = heads; A.groups = groups; A.N = N; A.P = P;
     A.a_per_row = a_per_row ? 1 : 0; A.q_scale = q_scale;
-    const int cols = OR_THREADS / L;
+    {   // slabs of R x C in registers: the largest slab that still gives every SM eight warps, else the smallest that fits
+        const int slabs[3][2] = {{8, 4}, {4, 4}, {2, 2}};
+        int pick = -1, pick_lr = 0;
+        for (int z = 0; z < 3; ++z) {
+            const int R = slabs[z][0], C = slabs[z][1];
+            if (P % C) continue;
+            int LR = 1;
+            while (LR * R < N) LR <<= 1;
+            if (LR > 32) continue;
+            pick = z; pick_lr = LR;
+            if ((long long)n_seqs * heads * LR * (P / C) / 32 >= 8LL * sms) break;
+        }
+        if (pick >= 0) {
+            const int R = slabs[pick][0], C = slabs[pick][1], LR = pick_lr;
+            int threads = LR * (P / C);
+            threads = threads > 256 ? 256 : ((threads + 31) & ~31);
+            auto ctas = [&](int th) { return (long long)((P / C + th / LR - 1) / (th / LR)) * heads * n_seqs; };
+            while (threads > 32 && (threads / 2) % 32 == 0 && ctas(threads) < 2LL * sms) threads >>= 1;
+            A.L = LR;
+            const int cols = (threads / LR) * C;
+            dim3 grid((P + cols - 1) / cols, heads, n_seqs);
+            const size_t smem = (size_t)OR_TILE * (2 * LR * R + (a_per_row ? LR * R : 1) + cols) * sizeof(float);
+            if (smem <= 200 * 1024) {
+#define KL_SLAB(TI, R_, C_)                                                                                          \
+    do {                                                                                                            \
+        if (smem > 48 * 1024)                                                                                       \
+            KL_CUDA(cudaFuncSetAttribute(outer_recurrence_slab_kernel<TI, R_, C_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        launch_kernel(outer_recurrence_slab_kernel<TI, R_, C_>, grid, threads, smem, stream, A);                    \
+    } while (0)
+#define KL_SLAB_BY(TI)                                                                                              \
+    do {                                                                                                            \
+        if (R == 8) KL_SLAB(TI, 8, 4); else if (R == 4) KL_SLAB(TI, 4, 4); else KL_SLAB(TI, 2, 2);                  \
+    } while (0)
+                if (in_dtype == KL_F32) KL_SLAB_BY(float); else KL_SLAB_BY(bf16);
+#undef KL_SLAB_BY
+#undef KL_SLAB
+                KL_LAUNCH_CHECK();
+                return KL_OK;
+            }
+        }
+    }
+    // any other size: a column of S over L lanes, rows of S in registers per thread at most 16 where 32 lanes allow it
+    int L = 1;
+    while (L < 32 && (N + L - 1) / L > 16) L <<= 1;
+    // and more lanes (fewer rows per thread) while the launch would leave the SMs short of warps: a prompt of one sequence
+    // is a chain of dependent steps per thread, and only other warps hide its latency
+    long long warps = (long long)n_seqs * heads * P * L / 32;
+    while (L < 32 && (N + L - 1) / L > 2 && warps < 24LL * sms) { L <<= 1; warps <<= 1; }
+    const int npt = (N + L - 1) / L;
+    A.L = L;
+    // the largest CTA that still leaves two CTAs per SM (a CTA loads a tile of tokens, waits, and computes: another one
+    // fills the wait), and no wider than the columns of S
+    int threads = OR_THREADS;
+    while (threads > 128 && (threads / 2 >= P * L || (long long)((P * L + threads - 1) / threads) * heads * n_seqs < 2LL * sms)) threads >>= 1;
+    const int cols = threads / L;
     dim3 grid((P + cols - 1) / cols, heads, n_seqs);
     const size_t smem = (size_t)OR_TILE * (2 * N + (a_per_row ? N : 1) + cols) * sizeof(float);
     if (smem > 200 * 1024) return KL_ERR_BAD_SIZE;
@@ -191,11 +354,11 @@ KL_API int kl_outer_recurrence(const void* q, long long ld_q, int q_col, const v
     do {                                                                                                            \
         if (smem > 48 * 1024)                                                                                       \
             KL_CUDA(cudaFuncSetAttribute(outer_recurrence_kernel<TI, NPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        launch_kernel(outer_recurrence_kernel<TI, NPT>, grid, OR_THREADS, smem, stream, A);                         \
+        launch_kernel(outer_recurrence_kernel<TI, NPT>, grid, threads, smem, stream, A);                         \
     } while (0)
 #define KL_OR_BY_NPT(TI)                                                                                            \
     do {                                                                                                            \
-        if (npt <= 4) KL_OR(TI, 4); else if (npt <= 8) KL_OR(TI, 8); else if (npt <= 16) KL_OR(TI, 16); else KL_OR(TI, 32); \
+        if (npt <= 2) KL_OR(TI, 2); else if (npt <= 4) KL_OR(TI, 4); else if (npt <= 8) KL_OR(TI, 8); else if (npt <= 16) KL_OR(TI, 16); else KL_OR(TI, 32); \
     } while (0)
     if (in_dtype == KL_F32) KL_OR_BY_NPT(float); else KL_OR_BY_NPT(bf16);
 #undef KL_OR_BY_NPT
