@@ -109,10 +109,10 @@ __device__ __forceinline__ void mt_copy_chunk_async(T* dst, const T* src, int G,
 __device__ __forceinline__ void mt_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void mt_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-template <typename T, int TQ, int PHASE>
+// UMAX: (head, 64 value columns) pieces of O per warp, TQ * UMAX <= 32 (phase 0 has none)
+template <typename T, int TQ, int UMAX, int PHASE>
 __global__ void __launch_bounds__(MT_THREADS, 1)
 attention_mixed_tiled_kernel(const MixedTiledArgs A) {
-    constexpr int UMAX = 32 / TQ;                          // (head, 64 value columns) pieces of O per warp
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(16) unsigned char mt_smem[];
@@ -461,16 +461,19 @@ KL_API int kl_attention_mixed_tiled(const void* q, long long q_stride, const voi
     A.keep_first = keep_first; A.splits = splits; A.qp = P.qp; A.kvp = P.kvp; A.vp = P.vp; A.pipelined = P.pipelined;
     A.scale = scale; A.softcap = softcap; A.out_scale = out_scale;
     const dim3 grid((max_new + P.tq - 1) / P.tq, n_seqs, splits);
-#define KL_MT(T, TQ)                                                                                                               \
+    const int per_warp = (heads * ((vdim + 63) / 64) + MT_WARPS - 1) / MT_WARPS;
+#define KL_MT(T, TQ, U)                                                                                                            \
     do {                                                                                                                           \
-        KL_CUDA(cudaFuncSetAttribute(attention_mixed_tiled_kernel<T, TQ, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P.smem)); \
-        KL_CUDA(cudaFuncSetAttribute(attention_mixed_tiled_kernel<T, TQ, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P.smem)); \
-        launch_kernel(attention_mixed_tiled_kernel<T, TQ, 0>, grid, MT_THREADS, P.smem, stream, A);                                \
-        launch_kernel(attention_mixed_tiled_kernel<T, TQ, 1>, grid, MT_THREADS, P.smem, stream, A);                                \
+        KL_CUDA(cudaFuncSetAttribute(attention_mixed_tiled_kernel<T, TQ, 1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P.smem)); \
+        KL_CUDA(cudaFuncSetAttribute(attention_mixed_tiled_kernel<T, TQ, U, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P.smem)); \
+        launch_kernel(attention_mixed_tiled_kernel<T, TQ, 1, 0>, grid, MT_THREADS, P.smem, stream, A);                             \
+        launch_kernel(attention_mixed_tiled_kernel<T, TQ, U, 1>, grid, MT_THREADS, P.smem, stream, A);                             \
     } while (0)
 #define KL_MT_BY_TQ(T)                                                                                                             \
     do {                                                                                                                           \
-        if (P.tq == 8) KL_MT(T, 8); else if (P.tq == 4) KL_MT(T, 4); else KL_MT(T, 1);                                             \
+        if (P.tq == 8) { if (per_warp <= 2) KL_MT(T, 8, 2); else KL_MT(T, 8, 4); }                                                 \
+        else if (P.tq == 4) { if (per_warp <= 2) KL_MT(T, 4, 2); else KL_MT(T, 4, 8); }                                            \
+        else { if (per_warp <= 2) KL_MT(T, 1, 2); else if (per_warp <= 8) KL_MT(T, 1, 8); else KL_MT(T, 1, 32); }                  \
     } while (0)
     if (dtype == KL_F32) KL_MT_BY_TQ(float); else KL_MT_BY_TQ(bf16);
 #undef KL_MT_BY_TQ

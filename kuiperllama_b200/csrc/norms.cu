@@ -285,7 +285,7 @@ head_rmsnorm_gate_kernel(const float* __restrict__ x, const T* __restrict__ gate
 
 // The same for long rows (a norm over hundreds of channels or more): one CTA per (token, head).
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 head_rmsnorm_gate_block_kernel(const float* __restrict__ x, const T* __restrict__ gate, long long gate_ld, const float* __restrict__ w,
                                T* __restrict__ out, long long out_ld, float out_scale, int heads, int dim, float eps, int gate_first,
                                int wide_weight) {
@@ -330,7 +330,7 @@ struct PairDelta {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 pair_rmsnorm_kernel(float* __restrict__ residual, const PairDelta d1, const PairDelta d2, const float* __restrict__ w1,
                     const float* __restrict__ w2, float eps, T* __restrict__ out1, T* __restrict__ out2, const int* __restrict__ rows,
                     int hidden) {
@@ -437,9 +437,9 @@ KL_API int kl_head_rmsnorm_gate(const float* x, const void* gate, long long gate
     const long long items = (long long)tokens * heads;
     if (dim >= 512) {
         if (dtype == KL_F32)
-            launch_kernel(head_rmsnorm_gate_block_kernel<float>, (int)items, 256, 0, stream, x, (const float*)gate, gate_ld, w, (float*)out, out_ld, out_scale, heads, dim, eps, gate_first, wide_weight);
+            launch_kernel(head_rmsnorm_gate_block_kernel<float>, (int)items, dim >= 2048 ? 1024 : 256, 0, stream, x, (const float*)gate, gate_ld, w, (float*)out, out_ld, out_scale, heads, dim, eps, gate_first, wide_weight);
         else if (dtype == KL_BF16)
-            launch_kernel(head_rmsnorm_gate_block_kernel<bf16>, (int)items, 256, 0, stream, x, (const bf16*)gate, gate_ld, w, (bf16*)out, out_ld, out_scale, heads, dim, eps, gate_first, wide_weight);
+            launch_kernel(head_rmsnorm_gate_block_kernel<bf16>, (int)items, dim >= 2048 ? 1024 : 256, 0, stream, x, (const bf16*)gate, gate_ld, w, (bf16*)out, out_ld, out_scale, heads, dim, eps, gate_first, wide_weight);
         else
             return KL_ERR_BAD_DTYPE;
         KL_LAUNCH_CHECK();
@@ -466,12 +466,14 @@ KL_API int kl_pair_rmsnorm(float* residual, const void* d1_rows, long long d1_ld
     PairDelta a{d1_rows, d1_ld, d1_pieces, d1_pieces ? d1_n : 0, d1_stride};
     PairDelta b{d2_rows, d2_ld, d2_pieces, d2_pieces ? d2_n : 0, d2_stride};
     const size_t smem = (size_t)hidden * sizeof(float);
+    // few rows: a row's loads (the stream, the rows or pieces of two results) are a chain per thread, so many threads
+    const int pair_threads = n_rows <= 64 && hidden >= 2048 ? 1024 : 256;
     if (dtype == KL_F32) {
         if (smem > 48 * 1024) KL_CUDA(cudaFuncSetAttribute(pair_rmsnorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        launch_kernel(pair_rmsnorm_kernel<float>, n_rows, 256, smem, stream, residual, a, b, w1, w2, eps, (float*)out1, (float*)out2, rows, hidden);
+        launch_kernel(pair_rmsnorm_kernel<float>, n_rows, pair_threads, smem, stream, residual, a, b, w1, w2, eps, (float*)out1, (float*)out2, rows, hidden);
     } else if (dtype == KL_BF16) {
         if (smem > 48 * 1024) KL_CUDA(cudaFuncSetAttribute(pair_rmsnorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        launch_kernel(pair_rmsnorm_kernel<bf16>, n_rows, 256, smem, stream, residual, a, b, w1, w2, eps, (bf16*)out1, (bf16*)out2, rows, hidden);
+        launch_kernel(pair_rmsnorm_kernel<bf16>, n_rows, pair_threads, smem, stream, residual, a, b, w1, w2, eps, (bf16*)out1, (bf16*)out2, rows, hidden);
     } else {
         return KL_ERR_BAD_DTYPE;
     }

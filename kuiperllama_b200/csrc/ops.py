@@ -816,7 +816,7 @@ def outer_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: torch
         _ptr(q), ctypes.c_longlong(q.stride(0)), 0, _ptr(k), ctypes.c_longlong(k.stride(0)), 0, _ptr(v), ctypes.c_longlong(v.stride(0)), 0,
         _ptr(a), ctypes.c_longlong(a.stride(0)), int(per_row), _ptr(c), ctypes.c_longlong(c.stride(0) if c is not None else 0), _ptr(skip),
         _ptr(state), ctypes.c_longlong(state.stride(0)), _ptr(y), ctypes.c_longlong(y.stride(0)), _ptr(step.cu_tokens),
-        _ptr(step.seq_slots), step.n_seqs, heads, groups, N, P, ctypes.c_float(q_scale), dtype_code(q.dtype), _stream()), "outer_recurrence")
+        _ptr(step.seq_slots), step.n_seqs, int(step.max_new), heads, groups, N, P, ctypes.c_float(q_scale), dtype_code(q.dtype), _stream()), "outer_recurrence")
 
 
 # --------------------------------------------------------------------------- attention with mixed heads
@@ -851,12 +851,15 @@ def mixed_attention_splits(n_seqs: int, context_class: int, window: int, keep_fi
 def attention_mixed(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     block_table: torch.Tensor, step, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, softcap: float = 0.0,
                     r1: Optional[torch.Tensor] = None, r2: Optional[torch.Tensor] = None, talk: Optional[torch.Tensor] = None,
-                    window: int = 0, keep_first: int = 0, out_scale: float = 1.0) -> None:
+                    window: int = 0, keep_first: int = 0, out_scale: float = 1.0, tiled: Optional[bool] = None,
+                    splits: Optional[int] = None) -> None:
     """Attention of every token of ``step`` over its sequence's cache with soft-capped scores, a distance bias
     r1_h ln(1 + r2_h (i - j)) taken off, a sliding window that also keeps the first ``keep_first`` keys, the heads' softmax
     weights mixed by ``talk`` [heads, heads], and head h's result times out_scale * sigmoid(gate[t, h]) (see
     attention_mixed.cu).  ``q`` [rows, heads * dim], ``gate`` [rows, heads], ``out`` [rows, heads * vdim]: the compute dtype,
-    any row stride."""
+    any row stride.  The tiled kernel (attention_mixed_tiled.cu) runs where its shared memory holds the sizes, else the
+    plain one; ``tiled=False`` asks for the plain one, and ``splits`` (1 to 32) sets into how many pieces a step of single
+    tokens cuts each sequence's keys instead of ``mixed_attention_splits``."""
     _cuda(q, gate, out, k_cache, v_cache, block_table, r1, r2, talk)
     _i32(block_table, "block_table")
     n = step.n_tokens
@@ -871,8 +874,12 @@ def attention_mixed(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Te
     _need(heads % kv_heads == 0, "attention_mixed: heads must be a multiple of kv heads")
     L = lib("attention_mixed_tiled")
     max_new = int(step.max_new)
-    if L.kl_attention_mixed_tiled_fits(heads, kv_heads, dim, vdim, dtype_code(q.dtype), int(talk is not None), max_new):
-        splits = mixed_attention_splits(step.n_seqs, getattr(step, "context_class", 0), window, keep_first) if max_new == 1 else 1
+    fits = L.kl_attention_mixed_tiled_fits(heads, kv_heads, dim, vdim, dtype_code(q.dtype), int(talk is not None), max_new)
+    _need(not (tiled and not fits), "attention_mixed: the tiled kernel cannot hold these sizes")
+    if fits and tiled is not False:
+        if splits is None:
+            splits = mixed_attention_splits(step.n_seqs, getattr(step, "context_class", 0), window, keep_first) if max_new == 1 else 1
+        _need(1 <= splits <= 32, "attention_mixed: 1 to 32 splits")
         ml = torch.empty((n, heads, splits, 2), dtype=torch.float32, device=q.device)
         part = torch.empty((n, splits, heads * vdim), dtype=torch.float32, device=q.device) if splits > 1 else None
         _check(L.kl_attention_mixed_tiled(

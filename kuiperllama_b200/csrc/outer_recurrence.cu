@@ -14,6 +14,7 @@
 //       through shared memory; per token every thread decays and updates its rows, multiplies them by q and the
 //       lanes' sums are added by shuffles.  Tokens are walked in order from the slot's state, so a result does not
 //       depend on how a prompt was cut.
+//   outer_recurrence_slab_kernel<TI, R, C>   the form that runs where the sizes allow: R x C of S per thread (see there).
 //   decay_softplus_kernel     dt = softplus(raw + bias), a = exp(-exp(A_log) dt) per (token, head), 32-bit.
 //   decay_lowrank_kernel      a = sigmoid(z)^(1 / tau) = exp(-softplus(-z) / tau), z = W2 r + b with r a short row per
 //                             token (the first of two projections, made with the mixer's other projections), 32-bit.
@@ -24,7 +25,7 @@
 namespace kl {
 
 constexpr int OR_THREADS = 512;          // the most threads of a CTA; a launch takes 128, 256 or 512
-constexpr int OR_TILE = 16;           // tokens per shared-memory tile
+constexpr int OR_TILE = 32;           // tokens per shared-memory tile
 
 struct OuterArgs {
     const void* q; long long ld_q; int q_col;        // [rows, >= q_col + groups * N]
@@ -37,6 +38,7 @@ struct OuterArgs {
     float* y; long long ld_y;                        // [rows, heads * P]
     const int* cu_tokens; const int* seq_slots;
     int heads, groups, N, P, L, a_per_row;
+    int vec_state;                                   // every row piece of four columns of S is 16-byte aligned
     float q_scale;
 };
 
@@ -166,37 +168,18 @@ outer_recurrence_slab_kernel(const OuterArgs A) {
 #pragma unroll
     for (int i = 0; i < R; ++i) {
         const int n = rg + LR * i;
+        if (C == 4 && A.vec_state && live && n < N) {                         // P and col0 are multiples of 4
+            const float4 v4 = *reinterpret_cast<const float4*>(S_slot + (size_t)n * P + col0);
+            S[i][0] = v4.x; S[i][1] = v4.y; S[i][2] = v4.z; S[i][C - 1] = v4.w;
+        } else {
 #pragma unroll
-        for (int j = 0; j < C; ++j) S[i][j] = (live && n < N) ? S_slot[(size_t)n * P + col0 + j] : 0.f;
+            for (int j = 0; j < C; ++j) S[i][j] = (live && n < N) ? S_slot[(size_t)n * P + col0 + j] : 0.f;
+        }
     }
     const TI* qp = (const TI*)A.q; const TI* kp = (const TI*)A.k; const TI* vp = (const TI*)A.v;
     const float skip = A.skip != nullptr ? A.skip[h] : 0.f;
-    for (int t0 = 0; t0 < n_new; t0 += OR_TILE) {
-        const int nt = min(OR_TILE, n_new - t0);
-        __syncthreads();
-#pragma unroll 4
-        for (int idx = threadIdx.x; idx < nt * Np; idx += threads) {
-            const int tt = idx / Np, j = idx - tt * Np;
-            const size_t row = (size_t)(row0 + t0 + tt);
-            float kv = 0.f, qv = 0.f;
-            if (j < N) {
-                kv = to_f32(kp[row * A.ld_k + A.k_col + (size_t)g * N + j]);
-                if (A.c != nullptr) kv *= A.c[row * A.ld_c + h];
-                qv = to_f32(qp[row * A.ld_q + A.q_col + (size_t)g * N + j]) * A.q_scale;
-            }
-            sm[tt * per_tok + j] = kv;
-            sm[tt * per_tok + Np + j] = qv;
-            if (A.a_per_row) sm[tt * per_tok + 2 * Np + j] = j < N ? A.a[row * A.ld_a + (size_t)h * N + j] : 0.f;
-        }
-        for (int idx = threadIdx.x; idx < nt * cols_per_cta; idx += threads) {
-            const int tt = idx / cols_per_cta, j = idx - tt * cols_per_cta;
-            const size_t row = (size_t)(row0 + t0 + tt);
-            const int cc = blockIdx.x * cols_per_cta + j;
-            sm[tt * per_tok + 2 * Np + a_len + j] = cc < P ? to_f32(vp[row * A.ld_v + A.v_col + (size_t)h * P + cc]) : 0.f;
-        }
-        if (!A.a_per_row)
-            for (int tt = threadIdx.x; tt < nt; tt += threads) sm[tt * per_tok + 2 * Np] = A.a[(size_t)(row0 + t0 + tt) * A.ld_a + h];
-        __syncthreads();
+    // one tile's tokens: decay, update, multiply by q, add the lanes' column sums
+    auto compute = [&](int t0, int nt) {
         for (int tt = 0; tt < nt; ++tt) {
             const float* kk = sm + tt * per_tok;
             const float* qq = kk + Np;
@@ -225,13 +208,45 @@ outer_recurrence_slab_kernel(const OuterArgs A) {
                 for (int j = 0; j < C; ++j) y[j] = fmaf(skip, v[j], acc[j]);
             }
         }
+    };
+    for (int t0 = 0; t0 < n_new; t0 += OR_TILE) {
+        const int nt = min(OR_TILE, n_new - t0);
+        __syncthreads();
+#pragma unroll 8
+        for (int idx = threadIdx.x; idx < nt * Np; idx += threads) {
+            const int tt = idx / Np, j = idx - tt * Np;
+            const size_t row = (size_t)(row0 + t0 + tt);
+            float kv = 0.f, qv = 0.f;
+            if (j < N) {
+                kv = to_f32(kp[row * A.ld_k + A.k_col + (size_t)g * N + j]);
+                if (A.c != nullptr) kv *= A.c[row * A.ld_c + h];
+                qv = to_f32(qp[row * A.ld_q + A.q_col + (size_t)g * N + j]) * A.q_scale;
+            }
+            sm[tt * per_tok + j] = kv;
+            sm[tt * per_tok + Np + j] = qv;
+            if (A.a_per_row) sm[tt * per_tok + 2 * Np + j] = j < N ? A.a[row * A.ld_a + (size_t)h * N + j] : 0.f;
+        }
+        for (int idx = threadIdx.x; idx < nt * cols_per_cta; idx += threads) {
+            const int tt = idx / cols_per_cta, j = idx - tt * cols_per_cta;
+            const size_t row = (size_t)(row0 + t0 + tt);
+            const int cc = blockIdx.x * cols_per_cta + j;
+            sm[tt * per_tok + 2 * Np + a_len + j] = cc < P ? to_f32(vp[row * A.ld_v + A.v_col + (size_t)h * P + cc]) : 0.f;
+        }
+        if (!A.a_per_row)
+            for (int tt = threadIdx.x; tt < nt; tt += threads) sm[tt * per_tok + 2 * Np] = A.a[(size_t)(row0 + t0 + tt) * A.ld_a + h];
+        __syncthreads();
+        compute(t0, nt);
     }
 #pragma unroll
     for (int i = 0; i < R; ++i) {
         const int n = rg + LR * i;
+        if (!(live && n < N)) continue;
+        if (C == 4 && A.vec_state) {
+            *reinterpret_cast<float4*>(S_slot + (size_t)n * P + col0) = make_float4(S[i][0], S[i][1], S[i][2], S[i][C - 1]);
+        } else {
 #pragma unroll
-        for (int j = 0; j < C; ++j)
-            if (live && n < N) S_slot[(size_t)n * P + col0 + j] = S[i][j];
+            for (int j = 0; j < C; ++j) S_slot[(size_t)n * P + col0 + j] = S[i][j];
+        }
     }
 }
 
@@ -279,7 +294,7 @@ using namespace kl;
 KL_API int kl_outer_recurrence(const void* q, long long ld_q, int q_col, const void* k, long long ld_k, int k_col, const void* v,
                                long long ld_v, int v_col, const float* a, long long ld_a, int a_per_row, const float* c,
                                long long ld_c, const float* skip, float* state, long long ld_state, float* y, long long ld_y,
-                               const int* cu_tokens, const int* seq_slots, int n_seqs, int heads, int groups, int N, int P,
+                               const int* cu_tokens, const int* seq_slots, int n_seqs, int max_new, int heads, int groups, int N, int P,
                                float q_scale, int in_dtype, cudaStream_t stream) {
     if (n_seqs <= 0) return KL_OK;
     if (heads <= 0 || groups <= 0 || heads % groups || N <= 0 || P <= 0 || N > 1024) return KL_ERR_BAD_SIZE;
@@ -292,6 +307,7 @@ KL_API int kl_outer_recurrence(const void* q, long long ld_q, int q_col, const v
     A.a = a; A.ld_a = ld_a; A.c = c; A.ld_c = ld_c; A.skip = skip; A.state = state; A.ld_state = ld_state; A.y = y; A.ld_y = ld_y;
     A.cu_tokens = cu_tokens; A.seq_slots = seq_slots; A.heads = heads; A.groups = groups; A.N = N; A.P = P;
     A.a_per_row = a_per_row ? 1 : 0; A.q_scale = q_scale;
+    A.vec_state = ((uintptr_t)state % 16 == 0 && ld_state % 4 == 0 && P % 4 == 0) ? 1 : 0;
     {   // slabs of R x C in registers: the largest slab that still gives every SM eight warps, else the smallest that fits
         const int slabs[3][2] = {{8, 4}, {4, 4}, {2, 2}};
         int pick = -1, pick_lr = 0;
@@ -309,7 +325,9 @@ KL_API int kl_outer_recurrence(const void* q, long long ld_q, int q_col, const v
             int threads = LR * (P / C);
             threads = threads > 256 ? 256 : ((threads + 31) & ~31);
             auto ctas = [&](int th) { return (long long)((P / C + th / LR - 1) / (th / LR)) * heads * n_seqs; };
-            while (threads > 32 && (threads / 2) % 32 == 0 && ctas(threads) < 2LL * sms) threads >>= 1;
+            // short runs (decode): smaller CTAs until every SM has two.  Long runs: a CTA's threads share the loading of
+            // each tile of tokens, which is the same for every column of a head, so the CTA stays wide
+            while (max_new <= 16 && threads > 32 && (threads / 2) % 32 == 0 && ctas(threads) < 2LL * sms) threads >>= 1;
             A.L = LR;
             const int cols = (threads / LR) * C;
             dim3 grid((P + cols - 1) / cols, heads, n_seqs);

@@ -181,7 +181,8 @@ def test_short_convolution_over_ragged_steps(dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H, G, N, Pd, per_row", [(6, 2, 12, 8, False), (3, 3, 20, 16, False), (4, 4, 8, 16, True), (5, 5, 33, 10, True),
-                                                   (8, 2, 64, 64, False), (2, 2, 128, 48, True), (1, 1, 1, 1, True)])
+                                                   (8, 2, 64, 64, False), (2, 2, 128, 48, True), (1, 1, 1, 1, True), (2, 1, 300, 4, False),
+                                                   (2, 2, 40, 7, True)])
 def test_matrix_state_recurrence_over_ragged_steps(dtype, H, G, N, Pd, per_row):
     """S_t = diag(a_t) S_(t-1) + (c_t k_t) v_t^T, y_t = S_t^T q_t + D v_t alone: one decay per head or one per row of the state,
     keys and queries shared by groups of heads, three sequences cut differently into two steps, then one token each."""
@@ -225,8 +226,10 @@ def test_matrix_state_recurrence_over_ragged_steps(dtype, H, G, N, Pd, per_row):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H, G, d, dv, window, keep", [(4, 2, 12, 20, 40, 5), (6, 6, 8, 8, 70, 0), (3, 1, 16, 12, 0, 0), (8, 2, 64, 32, 96, 16),
                                                         (16, 4, 32, 48, 130, 64), (2, 1, 16, 16, 64, 64), (5, 5, 10, 6, 1, 3)])
-def test_mixed_head_attention_on_scattered_pages(dtype, H, G, d, dv, window, keep):
-    """The attention kernel alone against the plain weights: prompts of unequal lengths on scattered pages, portions that start
+@pytest.mark.parametrize("tiled, splits", [(None, None), (None, 1), (None, 3), (False, None)])
+def test_mixed_head_attention_on_scattered_pages(dtype, H, G, d, dv, window, keep, tiled, splits):
+    """The attention kernels alone (the tiled one with its own choice of pieces for single tokens, with one piece and with
+    three, and the plain one) against the plain weights: prompts of unequal lengths on scattered pages, portions that start
     inside a page and inside the window, single tokens; soft cap, distance bias, mixing matrix and gate on and off."""
     from kuiperllama_b200.csrc import ops
     dt, dev = getattr(torch, dtype), "cuda:0"
@@ -263,7 +266,7 @@ def test_mixed_head_attention_on_scattered_pages(dtype, H, G, d, dv, window, kee
             out = torch.full((step.n_tokens, H * dv), 9.0, dtype=dt, device=dev)
             ops.attention_mixed(rows(qs), rows(gates) if full else None, out, kc, vc, table, step, H, G, d, dv, 0.3, 7.0 if full else 0.0,
                                 None if rr1 is None else rr1.to(dev), None if rr2 is None else rr2.to(dev), None if tk is None else tk.to(dev),
-                                window, keep, 1.25)
+                                window, keep, 1.25, tiled=tiled, splits=splits)
             ref = rows(want).to("cpu")
             assert torch.allclose(out.cpu().double(), ref, atol=tol, rtol=tol), (full, starts, news, float((out.cpu().double() - ref).abs().max()))
 
