@@ -39,6 +39,7 @@ struct OuterArgs {
     const int* cu_tokens; const int* seq_slots;
     int heads, groups, N, P, L, a_per_row;
     int vec_state;                                   // every row piece of four columns of S is 16-byte aligned
+    int vec_in;                                      // k, q and a can be read four elements at a time
     float q_scale;
 };
 
@@ -139,6 +140,16 @@ outer_recurrence_kernel(const OuterArgs A) {
     }
 }
 
+__device__ __forceinline__ void or_ld4(const float* p, float (&x)[4]) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+}
+__device__ __forceinline__ void or_ld4(const bf16* p, float (&x)[4]) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    x[0] = __uint_as_float(v.x << 16); x[1] = __uint_as_float(v.x & 0xffff0000u);
+    x[2] = __uint_as_float(v.y << 16); x[3] = __uint_as_float(v.y & 0xffff0000u);
+}
+
 // The same recurrence with R rows x C columns of S in a thread's registers: per token a thread reads R values each of
 // k, q (and a) and C of v for 3 R C multiply-adds, and only the column sums cross lanes.  A warp holds LR = 32 / CGW lanes
 // along the rows (lane = column group + CGW * row group; row n = row group + LR * i), so neighbouring lanes hold
@@ -148,7 +159,7 @@ __global__ void __launch_bounds__(256)
 outer_recurrence_slab_kernel(const OuterArgs A) {
     pdl_launch_dependents();
     pdl_wait();
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     const int s = blockIdx.z, h = blockIdx.y;
     const int row0 = A.cu_tokens[s], n_new = A.cu_tokens[s + 1] - row0;
     if (n_new <= 0) return;
@@ -161,7 +172,7 @@ outer_recurrence_slab_kernel(const OuterArgs A) {
     const int col0 = blockIdx.x * cols_per_cta + cg * C;
     const bool live = col0 < P;                                // P is a multiple of C
     const int g = h / (A.heads / A.groups);
-    const int a_len = A.a_per_row ? Np : 1;
+    const int a_len = A.a_per_row ? Np : 4;                    // one decay per head: a piece of four, so that rows stay aligned
     const int per_tok = 2 * Np + a_len + cols_per_cta;         // k (times c), q (times q_scale), a, v
     float* S_slot = A.state + (size_t)A.seq_slots[s] * A.ld_state + (size_t)h * N * P;
     float S[R][C];
@@ -212,6 +223,27 @@ outer_recurrence_slab_kernel(const OuterArgs A) {
     for (int t0 = 0; t0 < n_new; t0 += OR_TILE) {
         const int nt = min(OR_TILE, n_new - t0);
         __syncthreads();
+        if (A.vec_in) {                                        // four elements a turn; N, Np and per_tok are multiples of 4
+            const int quads = Np / 4;
+#pragma unroll 4
+            for (int idx = threadIdx.x; idx < nt * quads; idx += threads) {
+                const int tt = idx / quads, j = (idx - tt * quads) * 4;
+                const size_t row = (size_t)(row0 + t0 + tt);
+                float kv[4] = {0.f, 0.f, 0.f, 0.f}, qv[4] = {0.f, 0.f, 0.f, 0.f}, av[4] = {0.f, 0.f, 0.f, 0.f};
+                if (j < N) {
+                    or_ld4(kp + row * A.ld_k + A.k_col + (size_t)g * N + j, kv);
+                    or_ld4(qp + row * A.ld_q + A.q_col + (size_t)g * N + j, qv);
+                    const float cc = A.c != nullptr ? A.c[row * A.ld_c + h] : 1.0f;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) { kv[e] *= cc; qv[e] *= A.q_scale; }
+                    if (A.a_per_row) or_ld4(A.a + row * A.ld_a + (size_t)h * N + j, av);
+                }
+                float* dst = sm + tt * per_tok + j;
+                *reinterpret_cast<float4*>(dst) = make_float4(kv[0], kv[1], kv[2], kv[3]);
+                *reinterpret_cast<float4*>(dst + Np) = make_float4(qv[0], qv[1], qv[2], qv[3]);
+                if (A.a_per_row) *reinterpret_cast<float4*>(dst + 2 * Np) = make_float4(av[0], av[1], av[2], av[3]);
+            }
+        } else
 #pragma unroll 8
         for (int idx = threadIdx.x; idx < nt * Np; idx += threads) {
             const int tt = idx / Np, j = idx - tt * Np;
@@ -331,7 +363,12 @@ KL_API int kl_outer_recurrence(const void* q, long long ld_q, int q_col, const v
             A.L = LR;
             const int cols = (threads / LR) * C;
             dim3 grid((P + cols - 1) / cols, heads, n_seqs);
-            const size_t smem = (size_t)OR_TILE * (2 * LR * R + (a_per_row ? LR * R : 1) + cols) * sizeof(float);
+            const int per_tok = 2 * LR * R + (a_per_row ? LR * R : 4) + cols;
+            const size_t smem = (size_t)OR_TILE * per_tok * sizeof(float);
+            const int es = in_dtype == KL_F32 ? 4 : 2;
+            auto quad = [&](const void* p, long long ld, int col) { return (uintptr_t)p % (4 * es) == 0 && ld % 4 == 0 && col % 4 == 0; };
+            A.vec_in = (N % 4 == 0 && (LR * R) % 4 == 0 && per_tok % 4 == 0 && quad(q, ld_q, q_col) && quad(k, ld_k, k_col) &&
+                        (!a_per_row || ((uintptr_t)a % 16 == 0 && ld_a % 4 == 0))) ? 1 : 0;
             if (smem <= 200 * 1024) {
 #define KL_SLAB(TI, R_, C_)                                                                                          \
     do {                                                                                                            \
@@ -359,7 +396,7 @@ KL_API int kl_outer_recurrence(const void* q, long long ld_q, int q_col, const v
     long long warps = (long long)n_seqs * heads * P * L / 32;
     while (L < 32 && (N + L - 1) / L > 2 && warps < 24LL * sms) { L <<= 1; warps <<= 1; }
     const int npt = (N + L - 1) / L;
-    A.L = L;
+    A.L = L; A.vec_in = 0;
     // the largest CTA that still leaves two CTAs per SM (a CTA loads a tile of tokens, waits, and computes: another one
     // fills the wait), and no wider than the columns of S
     int threads = OR_THREADS;
