@@ -10,7 +10,8 @@
 // have `dim` and values `vdim` elements per head (two cache tensors of their own shapes).  Everything is computed
 // in 32 bits from the stored keys and values; the compute dtype is only what q, the cache and the output hold.
 //
-//   attention_mixed_kernel<T>   a CTA per token with all its heads.  Because w mixes normalised weights of all heads
+//   attention_mixed_kernel<T>   the plain form (attention_mixed_tiled.cu runs wherever its shared memory holds the sizes):
+//       a CTA per token with all its heads.  Because w mixes normalised weights of all heads
 //       at the same key, the keys are walked twice, in chunks of 32 by absolute position: once for every head's
 //       maximum and sum, once more for p, the mix and the product with the values.  The chunks and the order of the
 //       sums depend on positions only, so a row's result does not depend on the step it arrived in.  Pages wholly
