@@ -11,6 +11,9 @@ execution of a layer that asks for them, and fixed-size state per slot.
   the window still touches: before a step, the pages of a sequence that lie wholly below
   ``length - window + 1`` go back to the group's pool (no query of this or a later step reads
   them), so such a group can be given a smaller pool (``window_step_tokens``).
+* A group of kind "pooled" keeps, beside the window's pages, one float32 row per kv head for every complete
+  block of ``pool`` positions (the mean of the block's keys, and of its values) in pages of a second pool;
+  those rows stay as long as the sequence lives.
 * Beside the pages every execution may ask for per-slot state of a fixed shape (a
   recurrent mixer's state, for instance).  It is zeroed when a slot is handed out.  The
   dense Llama decoder asks for none.
@@ -37,13 +40,15 @@ class KVRequest:
     ``window`` is the number of most recent keys the mixer reads (None: all); with a window
     the pages that no query can reach any more are given back while the sequence grows, except
     those that hold any of the first ``keep_first`` keys (a window that also keeps the sequence's
-    first tokens).  ``value_dim``: the size of a value row where it differs from a key's."""
+    first tokens).  ``value_dim``: the size of a value row where it differs from a key's.  ``pool`` (kind
+    "pooled"): positions per block whose mean key and value are kept once the block is complete."""
     kv_heads: int
     head_dim: int
     kind: str = "full"
     window: Optional[int] = None
     value_dim: Optional[int] = None
     keep_first: int = 0
+    pool: int = 0
 
 
 @dataclass(frozen=True)
@@ -61,6 +66,16 @@ class CacheView:
     block_table: Optional[torch.Tensor]   # int32 [slots, blocks_per_seq] of the group
     state: Optional[torch.Tensor]         # [slots, *shape] or None
     writable: bool                        # False: the execution reads another one's cache
+    pooled: Optional["PooledView"] = None # kind "pooled": the means of complete blocks
+
+
+@dataclass
+class PooledView:
+    """Rows of block means: row b of a sequence lies in page ``block_table[slot, b // PAGE]`` at place b % PAGE."""
+    k: torch.Tensor                       # float32 [pages, kv_heads, PAGE, head_dim]
+    v: torch.Tensor                       # float32 [pages, kv_heads, PAGE, value_dim]
+    block_table: torch.Tensor             # int32 [slots, blocks_per_seq]
+    pool: int                             # positions per block
 
 
 _KINDS: Dict[str, type] = {}
@@ -74,7 +89,7 @@ def register_cache_kind(name: str):
     * ``reserve(slot, old_length, new_length)``: room for the sequence to grow (raises CacheError),
     * ``release(slot)``: everything the sequence holds goes back,
     * ``flush()``: bring device-side tables up to date on the current stream,
-    * ``view(j) -> (k, v, block_table)``: what execution ``entries[j]`` sees,
+    * ``view(j) -> (k, v, block_table)`` or ``(k, v, block_table, pooled)``: what execution ``entries[j]`` sees,
     * ``held() -> int`` and ``pool_size() -> int`` for the accounting, ``bytes() -> int``.
     """
     def deco(cls: type) -> type:
@@ -105,7 +120,7 @@ class PagedGroup:
         self.entries = entries
         if request.window is not None and window_step_tokens is not None:
             # the window's keys and the step's new tokens, both possibly straddling page borders
-            per_slot = pages_for(request.window + window_step_tokens, PAGE) + 1 + pages_for(request.keep_first, PAGE)
+            per_slot = pages_for(self.window_tokens() + window_step_tokens, PAGE) + 1 + pages_for(request.keep_first, PAGE)
             n_pages = max(1, min(n_pages, n_slots * per_slot))
         self.pages = FreeList(n_pages, "page")
         self.blocks_per_seq = blocks_per_seq
@@ -132,7 +147,7 @@ class PagedGroup:
         if self.request.window is not None:
             # the first key any query of this step (positions old_length and up) or of a later
             # one reads is old_length - window + 1: whole blocks below it go back to the pool
-            keep_from = min(max(0, old_length - self.request.window + 1) // PAGE, len(have))
+            keep_from = min(self.first_needed(old_length) // PAGE, len(have))
             kept_first = pages_for(self.request.keep_first, PAGE)      # blocks that hold kept first keys stay
             for b in range(max(self.first_block[slot], kept_first), keep_from):
                 self.pages.give_back(have[b])
@@ -145,6 +160,14 @@ class PagedGroup:
                 self.table_host[slot, len(have)] = p
                 have.append(p)
             self.dirty.add(slot)
+
+    def first_needed(self, old_length: int) -> int:
+        """The first position a step that starts at ``old_length``, or a later one, still reads (with a window)."""
+        return max(0, old_length - self.request.window + 1)
+
+    def window_tokens(self) -> int:
+        """Tokens before a step's first that the group keeps per sequence (with a window)."""
+        return self.request.window
 
     def release(self, slot: int) -> None:
         for p in reversed(self.pages_of(slot)):
@@ -179,6 +202,71 @@ class KeysOnlyGroup(PagedGroup):
     for this kind; its view's ``v`` is the key tensor itself."""
 
     stores_values = False
+
+
+@register_cache_kind("pooled")
+class PooledWindowGroup(PagedGroup):
+    """A window of keys and values in pages, as ``PagedGroup`` keeps them, and beside it the means of whole blocks:
+    for every complete block of ``request.pool`` positions one float32 key row and one float32 value row per kv head
+    (written by the mixer's kernel when the block's last position arrives), in pages of ``PAGE`` rows from a second
+    pool with a block table of its own.  A block's positions stay in the window's pages until the block is complete,
+    also where the window is shorter than a block; the means stay until the sequence ends."""
+
+    def __init__(self, request: KVRequest, entries: List[int], n_pages: int, n_slots: int, blocks_per_seq: int,
+                 dtype: torch.dtype, device: torch.device, window_step_tokens: Optional[int] = None):
+        if request.pool < 1:
+            raise CacheError(f"a pooled cache needs a block size of at least one position, got {request.pool}")
+        if request.window is None or request.keep_first:
+            raise CacheError("a pooled cache keeps a window of recent keys and no first keys")
+        super().__init__(request, entries, n_pages, n_slots, blocks_per_seq, dtype, device, window_step_tokens)
+        P = request.pool
+        # every live sequence of L tokens holds L // P rows, in whole pages
+        self.pool_blocks_per_seq = pages_for(max(1, blocks_per_seq * PAGE // P), PAGE)
+        n_pool_pages = max(1, min(n_slots * self.pool_blocks_per_seq, pages_for(n_pages * PAGE // P, PAGE) + n_slots))
+        self.pool_pages = FreeList(n_pool_pages, "page of block means")
+        shape = (len(entries), n_pool_pages, request.kv_heads, PAGE)
+        self.pool_k = torch.zeros(shape + (request.head_dim,), dtype=torch.float32, device=device)
+        self.pool_v = torch.zeros(shape + (request.value_dim or request.head_dim,), dtype=torch.float32, device=device)
+        self.pool_table_host = torch.zeros((n_slots, self.pool_blocks_per_seq), dtype=torch.int32)
+        self.pool_table = torch.zeros((n_slots, self.pool_blocks_per_seq), dtype=torch.int32, device=device)
+        self.pool_slot_pages: List[List[int]] = [[] for _ in range(n_slots)]
+        self.pool_dirty: set = set()
+
+    def first_needed(self, old_length: int) -> int:
+        # the window's first key, or the first position of the block that is still being filled
+        return min(max(0, old_length - self.request.window + 1), old_length // self.request.pool * self.request.pool)
+
+    def window_tokens(self) -> int:
+        return self.request.window + self.request.pool
+
+    def reserve(self, slot: int, old_length: int, new_length: int) -> None:
+        super().reserve(slot, old_length, new_length)
+        have = self.pool_slot_pages[slot]
+        need = pages_for(new_length // self.request.pool, PAGE)
+        if need > len(have):
+            for p in self.pool_pages.take_many(need - len(have)):
+                self.pool_table_host[slot, len(have)] = p
+                have.append(p)
+            self.pool_dirty.add(slot)
+
+    def release(self, slot: int) -> None:
+        super().release(slot)
+        for p in reversed(self.pool_slot_pages[slot]):
+            self.pool_pages.give_back(p)
+        self.pool_slot_pages[slot] = []
+
+    def flush(self) -> None:
+        super().flush()
+        if self.pool_dirty:
+            lo, hi = min(self.pool_dirty), max(self.pool_dirty) + 1
+            self.pool_table[lo:hi].copy_(self.pool_table_host[lo:hi], non_blocking=True)
+            self.pool_dirty.clear()
+
+    def view(self, j: int):
+        return self.k[j], self.v[j], self.table, PooledView(self.pool_k[j], self.pool_v[j], self.pool_table, self.request.pool)
+
+    def bytes(self) -> int:
+        return super().bytes() + 4 * (self.pool_k.numel() + self.pool_v.numel())
 
 
 class SequenceCache:
@@ -270,11 +358,12 @@ class SequenceCache:
     def view(self, entry: int) -> CacheView:
         src = self.cache_from[entry]
         owner = entry if src is None else src
-        k = v = table = None
+        k = v = table = pooled = None
         if owner in self._where:
             g, j = self._where[owner]
-            k, v, table = g.view(j)
-        return CacheView(k=k, v=v, block_table=table, state=self.states.get(owner), writable=src is None)
+            k, v, table, *more = g.view(j)
+            pooled = more[0] if more else None
+        return CacheView(k=k, v=v, block_table=table, state=self.states.get(owner), writable=src is None, pooled=pooled)
 
     # ------------------------------------------------------------------ accounting
     def held_tokens(self) -> int:

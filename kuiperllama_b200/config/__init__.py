@@ -6,7 +6,8 @@ from .llama import Llama3RopeScaling, LlamaConfig
 from .terolix import TerolixConfig
 from .munadra import MunadraConfig
 from .bededra import BededraConfig
+from .dofevik import DofevikConfig
 
 __all__ = ["ConfigError", "config_class", "config_from_dict", "config_from_file", "config_from_folder",
            "known_architectures", "register_architecture", "LayerSpec", "ModelSpec", "PartSpec",
-           "ScheduleEntry", "default_schedule", "Llama3RopeScaling", "LlamaConfig", "TerolixConfig", "MunadraConfig", "BededraConfig"]
+           "ScheduleEntry", "default_schedule", "Llama3RopeScaling", "LlamaConfig", "TerolixConfig", "MunadraConfig", "BededraConfig", "DofevikConfig"]

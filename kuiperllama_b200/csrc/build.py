@@ -46,6 +46,8 @@ SOURCES: Dict[str, str] = {
     "outer_recurrence": "outer_recurrence.cu",
     "attention_mixed": "attention_mixed.cu",
     "attention_mixed_tiled": "attention_mixed_tiled.cu",
+    "qk_prepare": "qk_prepare.cu",
+    "attention_pooled": "attention_pooled.cu",
 }
 HEADERS: List[str] = ["common.cuh", "tcgen05.cuh", "tma_host.cuh", "attention_decode_noalloc.h"]
 

@@ -9,7 +9,8 @@
 //     fills with W_uk^T q (the unrotated part taken through the key up-projection, so that scores are
 //     plain dot products with cache rows).
 //
-// A layer that reads another layer's latent runs the query part alone (kv_col < 0).  Rotation: pair i of
+// A layer that reads another layer's latent runs the query part alone (kv_col < 0).  The queries may lie in a
+// matrix of their own (`qsrc`, rows `q_ld` apart: queries that came through a latent and a second product).  Rotation: pair i of
 // the first rot_dims elements is (2i, 2i+1) (interleaved) or (i, i + rot_dims/2); angle = position *
 // inv_freq[i] in 32 bits, and cos and sin are multiplied by `mscale` (1 without frequency scaling).
 // ExiledOfCode/KuiperLLama rotates whole heads of q and k from tables (rope_kernel.cu:38-49,124-135).
@@ -37,7 +38,7 @@ __device__ __forceinline__ void rotate_into(const T* __restrict__ src, T* __rest
 
 template <typename T>
 __global__ void __launch_bounds__(128)
-latent_prepare_kernel(const T* __restrict__ proj, long long ld, int q_col, int kv_col, const float* __restrict__ norm_w, float eps,
+latent_prepare_kernel(const T* __restrict__ proj, long long ld, const T* __restrict__ qsrc, long long q_ld, int q_col, int kv_col, const float* __restrict__ norm_w, float eps,
                       const float* __restrict__ inv_freq, int rot_dims, float mscale, int interleaved,
                       const int* __restrict__ positions, const int* __restrict__ token_slot,
                       const int* __restrict__ block_table, int blocks_per_seq, T* __restrict__ cache, T* __restrict__ qfull,
@@ -62,7 +63,7 @@ latent_prepare_kernel(const T* __restrict__ proj, long long ld, int q_col, int k
     const int Dk = kv_rank + rot_dim, pairs = (rot_dim + 1) / 2;
     for (int e = threadIdx.x; e < H * pairs; e += blockDim.x) {
         const int h = e / pairs, i = e % pairs;
-        rotate_into(row + q_col + (size_t)h * (dim + rot_dim) + dim, qfull + ((size_t)t * H + h) * Dk + kv_rank, rot_dim, rot_dims,
+        rotate_into(qsrc + (size_t)t * q_ld + q_col + (size_t)h * (dim + rot_dim) + dim, qfull + ((size_t)t * H + h) * Dk + kv_rank, rot_dim, rot_dims,
                     cs, interleaved, i);
     }
     if (kv_col < 0) return;
@@ -80,21 +81,22 @@ latent_prepare_kernel(const T* __restrict__ proj, long long ld, int q_col, int k
 
 using namespace kl;
 
-KL_API int kl_latent_prepare(const void* proj, long long ld, int q_col, int kv_col, const float* norm_w, float eps,
+KL_API int kl_latent_prepare(const void* proj, long long ld, const void* qsrc, long long q_ld, int q_col, int kv_col, const float* norm_w, float eps,
                              const float* inv_freq, int rot_dims, float mscale, int interleaved, const int* positions,
                              const int* token_slot, const int* block_table, int blocks_per_seq, void* cache, void* qfull,
                              int n_tokens, int H, int dim, int rot_dim, int kv_rank, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return KL_OK;
     if (rot_dims % 2 || rot_dims > rot_dim || rot_dims < 0 || H <= 0 || kv_rank <= 0 || dim < 0) return KL_ERR_BAD_SIZE;
     if (rot_dims > 0 && inv_freq == nullptr) return KL_ERR_BAD_SIZE;
+    if (qsrc == nullptr) return KL_ERR_BAD_SIZE;
     if (kv_col >= 0 && (cache == nullptr || norm_w == nullptr || block_table == nullptr)) return KL_ERR_BAD_SIZE;
     const size_t smem = (size_t)(rot_dims + 33) * sizeof(float);
     if (dtype == KL_F32)
-        launch_kernel(latent_prepare_kernel<float>, n_tokens, 128, smem, stream, (const float*)proj, ld, q_col, kv_col, norm_w, eps,
+        launch_kernel(latent_prepare_kernel<float>, n_tokens, 128, smem, stream, (const float*)proj, ld, (const float*)qsrc, q_ld, q_col, kv_col, norm_w, eps,
                       inv_freq, rot_dims, mscale, interleaved, positions, token_slot, block_table, blocks_per_seq, (float*)cache,
                       (float*)qfull, H, dim, rot_dim, kv_rank);
     else if (dtype == KL_BF16)
-        launch_kernel(latent_prepare_kernel<bf16>, n_tokens, 128, smem, stream, (const bf16*)proj, ld, q_col, kv_col, norm_w, eps,
+        launch_kernel(latent_prepare_kernel<bf16>, n_tokens, 128, smem, stream, (const bf16*)proj, ld, (const bf16*)qsrc, q_ld, q_col, kv_col, norm_w, eps,
                       inv_freq, rot_dims, mscale, interleaved, positions, token_slot, block_table, blocks_per_seq, (bf16*)cache,
                       (bf16*)qfull, H, dim, rot_dim, kv_rank);
     else

@@ -1,8 +1,9 @@
 // Routing for a mixture of experts: who goes where, and the weighted sum at the end.
 //
-//   moe_route_kernel    a warp per token: s = softmax(z) over all experts in 32 bits, the `top` largest
-//                       (the lower index among equals), their scores as weights (divided by their sum
-//                       if asked).
+//   moe_route_kernel    a warp per token: s = softmax(z) over all experts in 32 bits (z plus a bias per expert
+//                       where one is given), the `top` largest (the lower index among equals), their scores
+//                       as weights (divided by their sum if asked, which is the softmax over the chosen
+//                       logits alone).
 //   moe_plan_kernel     one CTA: counts per expert, a list of (token, choice) pairs sorted by expert in
 //                       which every expert's run is padded to whole tiles, the expert of every tile, and
 //                       each pair's place in the list.  Everything stays on the device, so a step with
@@ -22,7 +23,7 @@ constexpr int MOE_PLAN_THREADS = 1024;
 constexpr int MOE_MAX_EXPERTS = 32 * MOE_MAX_PER_LANE;
 
 __global__ void __launch_bounds__(128)
-moe_route_kernel(const float* __restrict__ logits, long long ld, int tokens, int experts, int top, int renormalise,
+moe_route_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ bias, int tokens, int experts, int top, int renormalise,
                  int groups, int keep_groups, float renorm_eps, int* __restrict__ choice, float* __restrict__ weight) {
     pdl_launch_dependents();
     pdl_wait();
@@ -36,7 +37,7 @@ moe_route_kernel(const float* __restrict__ logits, long long ld, int tokens, int
 #pragma unroll
     for (int i = 0; i < MOE_MAX_PER_LANE; ++i) {
         const int e = lane + 32 * i;
-        s[i] = e < experts ? z[e] : -INFINITY;
+        s[i] = e < experts ? (bias ? z[e] + bias[e] : z[e]) : -INFINITY;
         m = fmaxf(m, s[i]);
     }
     m = warp_max(m);
@@ -199,12 +200,12 @@ KL_API int kl_moe_gather(const void* x, long long ld, const int* list_rows, int 
     return KL_OK;
 }
 
-KL_API int kl_moe_route(const float* logits, long long ld, int tokens, int experts, int top, int renormalise, int groups,
+KL_API int kl_moe_route(const float* logits, long long ld, const float* bias, int tokens, int experts, int top, int renormalise, int groups,
                         int keep_groups, float renorm_eps, int* choice, float* weight, cudaStream_t stream) {
     if (tokens <= 0) return KL_OK;
     if (experts <= 0 || experts > MOE_MAX_EXPERTS || top <= 0 || top > experts) return KL_ERR_BAD_SIZE;
     if (groups < 1 || experts % groups || keep_groups < 1 || keep_groups > groups || top > keep_groups * (experts / groups)) return KL_ERR_BAD_SIZE;
-    launch_kernel(moe_route_kernel, (tokens + 3) / 4, 128, 0, stream, logits, ld, tokens, experts, top, renormalise, groups, keep_groups,
+    launch_kernel(moe_route_kernel, (tokens + 3) / 4, 128, 0, stream, logits, ld, bias, tokens, experts, top, renormalise, groups, keep_groups,
                   renorm_eps, choice, weight);
     KL_LAUNCH_CHECK();
     return KL_OK;

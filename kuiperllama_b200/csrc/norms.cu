@@ -456,6 +456,41 @@ KL_API int kl_head_rmsnorm_gate(const float* x, const void* gate, long long gate
     return KL_OK;
 }
 
+// RMS norm of rows in the compute dtype that are no part of the residual stream (a latent between two products):
+// out[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w, statistics in 32 bits; rows of x may be `x_ld` elements apart.
+namespace kl {
+template <typename T>
+__global__ void __launch_bounds__(256)
+rows_rmsnorm_kernel(const T* __restrict__ x, long long x_ld, const float* __restrict__ w, T* __restrict__ out, long long out_ld,
+                    int width, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const T* row = x + (size_t)blockIdx.x * x_ld;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) { const float v = to_f32(row[i]); ss += v * v; }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    T* o = out + (size_t)blockIdx.x * out_ld;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = from_f32<T>(to_f32(row[i]) * inv * (w ? w[i] : 1.f));
+}
+}  // namespace kl
+
+KL_API int kl_rows_rmsnorm(const void* x, long long x_ld, const float* w, void* out, long long out_ld, int rows, int width, float eps,
+                           int dtype, cudaStream_t stream) {
+    if (rows <= 0) return KL_OK;
+    if (width <= 0) return KL_ERR_BAD_SIZE;
+    const int threads = width >= 1024 ? 256 : 128;
+    if (dtype == KL_F32)
+        launch_kernel(rows_rmsnorm_kernel<float>, rows, threads, 0, stream, (const float*)x, x_ld, w, (float*)out, out_ld, width, eps);
+    else if (dtype == KL_BF16)
+        launch_kernel(rows_rmsnorm_kernel<bf16>, rows, threads, 0, stream, (const bf16*)x, x_ld, w, (bf16*)out, out_ld, width, eps);
+    else
+        return KL_ERR_BAD_DTYPE;
+    KL_LAUNCH_CHECK();
+    return KL_OK;
+}
+
 // d*_rows: compute dtype; d*_pieces: float32 [S, n, hidden].  out2 may be null; with `rows` the stream is not written.
 KL_API int kl_pair_rmsnorm(float* residual, const void* d1_rows, long long d1_ld, const float* d1_pieces, int d1_n, long long d1_stride,
                            const void* d2_rows, long long d2_ld, const float* d2_pieces, int d2_n, long long d2_stride,

@@ -243,6 +243,18 @@ def head_rmsnorm_gate(x: torch.Tensor, gate: Optional[torch.Tensor], weight: Opt
                                              dtype_code(out.dtype), _stream()), "head_rmsnorm_gate")
 
 
+def rows_rmsnorm(x: torch.Tensor, weight: Optional[torch.Tensor], out: torch.Tensor, eps: float) -> None:
+    """out[t] = x[t] / sqrt(mean(x[t]^2) + eps) * weight for rows in the compute dtype (any row stride) that are no part of the
+    residual stream; statistics in 32 bits, ``weight`` float32 [width] or None."""
+    _cuda(x, weight, out)
+    n, width = x.shape
+    _columns(x, n, width, "rows_rmsnorm: x"); _columns(out, n, width, "rows_rmsnorm: out")
+    _need(x.dtype == out.dtype, "rows_rmsnorm: dtypes differ")
+    _need(weight is None or (weight.dtype == torch.float32 and weight.is_contiguous() and weight.numel() == width), "rows_rmsnorm: weight")
+    _check(lib("norms").kl_rows_rmsnorm(_ptr(x), ctypes.c_longlong(x.stride(0)), _ptr(weight), _ptr(out), ctypes.c_longlong(out.stride(0)),
+                                        n, width, ctypes.c_float(eps), dtype_code(x.dtype), _stream()), "rows_rmsnorm")
+
+
 def pair_rmsnorm(residual: torch.Tensor, deltas, w1: Optional[torch.Tensor], w2: Optional[torch.Tensor], out1: Optional[torch.Tensor],
                  out2: Optional[torch.Tensor], eps: float, rows: Optional[torch.Tensor] = None, dtype: Optional[torch.dtype] = None) -> None:
     """x = residual + (d1 + d2), written back unless ``rows``; out1 = x / rms(x) * w1, out2 = x / rms(x) * w2 (one root mean
@@ -426,6 +438,96 @@ def attention_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: t
                                                    dtype_code(q.dtype), _stream()), "attention_simt")
 
 
+def qk_prepare(proj: torch.Tensor, q_col: int, k_col: int, v_col: Optional[int], positions: torch.Tensor, token_slot: torch.Tensor,
+               block_table: Optional[torch.Tensor], k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], n_tokens: int,
+               num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, *, q_bias: Optional[torch.Tensor] = None,
+               k_bias: Optional[torch.Tensor] = None, v_bias: Optional[torch.Tensor] = None, inv_freq: Optional[torch.Tensor] = None,
+               rotary_dim: int = 0, interleaved: bool = False, head_norm: bool = False, eps: float = 0.0,
+               q_norm_weight: Optional[torch.Tensor] = None, k_norm_weight: Optional[torch.Tensor] = None) -> None:
+    """For every token of ``proj`` [tokens, ...] (q heads from column ``q_col``, k heads from ``k_col``, v heads from ``v_col``):
+    add the biases (float32), turn the first ``rotary_dim`` elements of every q and k head by the position (pairs (2i, 2i + 1)
+    if ``interleaved``, else (i, i + rotary_dim / 2)), with ``head_norm`` divide every q and k head by its root mean square
+    (``eps`` inside the root) and multiply by ``q_norm_weight`` / ``k_norm_weight`` (float32 [head_dim]) where given; q goes back
+    in place, k into ``k_cache`` [pages, KV, PAGE, head_dim], v into ``v_cache`` [pages, KV, PAGE, value_dim].  ``v_col`` None:
+    the key heads as projected (with bias, before rotation and norm) are the values.  Both caches None: only q is made."""
+    _cuda(proj, positions, token_slot, block_table, k_cache, v_cache, q_bias, k_bias, v_bias, inv_freq, q_norm_weight, k_norm_weight)
+    _i32(positions, "positions"); _i32(token_slot, "token_slot"); _i32(block_table, "block_table")
+    H, KV, hd, vd = num_heads, num_kv_heads, head_dim, value_dim
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[0] >= n_tokens, "qk_prepare: projections")
+    _need(q_col + H * hd <= proj.shape[1] and k_col + KV * hd <= proj.shape[1] and (v_col is None or v_col + KV * vd <= proj.shape[1]),
+          "qk_prepare: columns")
+    _need(positions.numel() >= n_tokens and token_slot.numel() >= n_tokens, "qk_prepare: one position and slot per token")
+    for b, size, name in ((q_bias, H * hd, "q_bias"), (k_bias, KV * hd, "k_bias"), (v_bias, KV * vd, "v_bias"),
+                          (q_norm_weight, hd, "q_norm_weight"), (k_norm_weight, hd, "k_norm_weight")):
+        _need(b is None or (b.dtype == torch.float32 and b.is_contiguous() and b.numel() == size), f"qk_prepare: {name} must be float32 [{size}]")
+    _need(rotary_dim == 0 or (inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rotary_dim // 2),
+          "qk_prepare: inv_freq must be float32 [rotary_dim / 2]")
+    _need((k_cache is None) == (v_cache is None), "qk_prepare: both caches or none")
+    if k_cache is not None:
+        _need(block_table is not None and k_cache.dtype == proj.dtype == v_cache.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+              and tuple(k_cache.shape[1:]) == (KV, PAGE, hd) and tuple(v_cache.shape[1:]) == (KV, PAGE, vd), "qk_prepare: cache layout")
+    _need(v_col is not None or vd == hd, "qk_prepare: values that are keys have the keys' size")
+    _check(lib("qk_prepare").kl_qk_prepare(
+        _ptr(proj), ctypes.c_longlong(proj.stride(0)), q_col, k_col, -1 if v_col is None else v_col, _ptr(q_bias), _ptr(k_bias), _ptr(v_bias),
+        _ptr(inv_freq), int(rotary_dim), int(bool(interleaved)), int(bool(head_norm)), ctypes.c_float(eps), _ptr(q_norm_weight),
+        _ptr(k_norm_weight), _ptr(positions), _ptr(token_slot), _ptr(block_table), 0 if block_table is None else block_table.shape[1],
+        _ptr(k_cache), _ptr(v_cache), n_tokens, H, KV, hd, vd, dtype_code(proj.dtype), _stream()), "qk_prepare")
+
+
+ATTENTION_WEIGHTS = {"softmax": 0, "sigmoid": 1}
+
+
+def attention_pooled(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                     positions: torch.Tensor, token_slot: torch.Tensor, n_tokens: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                     value_dim: int, scale: float, window: int, *, weights: str = "softmax", sink: Optional[torch.Tensor] = None,
+                     head_bias: Optional[torch.Tensor] = None, pooled=None) -> None:
+    """out[t, h] = sum over what token t sees of weight * value: the keys of the last ``window`` positions (0: all) and, with
+    ``pooled`` (k, v float32 [pages, KV, PAGE, dim], block_table, pool), the mean key and value of every block of ``pool``
+    positions that lies wholly before the window.  ``weights`` "softmax" (``sink``: float32 [heads] in the denominator) or
+    "sigmoid" (sigmoid(score + head_bias[h]), not normalised).  ``q`` [tokens, >= heads * head_dim] with any row stride."""
+    pk = pv = pt = None
+    pool = 0
+    if pooled is not None:
+        pk, pv, pt, pool = pooled.k, pooled.v, pooled.block_table, int(pooled.pool)
+    _cuda(q, out, k_cache, v_cache, block_table, positions, token_slot, sink, head_bias, pk, pv, pt)
+    _i32(positions, "positions"); _i32(token_slot, "token_slot"); _i32(block_table, "block_table"); _i32(pt, "pooled block_table")
+    H, KV, hd, vd = num_heads, num_kv_heads, head_dim, value_dim
+    _need(q.dim() == 2 and q.stride(1) == 1 and q.shape[1] >= H * hd and q.shape[0] >= n_tokens, "attention_pooled: q")
+    _need(out.is_contiguous() and out.shape[0] >= n_tokens and out.shape[1] == H * vd, "attention_pooled: out shape")
+    _need(q.dtype == out.dtype == k_cache.dtype == v_cache.dtype, "attention_pooled: dtypes differ")
+    _need(k_cache.is_contiguous() and v_cache.is_contiguous() and tuple(k_cache.shape[1:]) == (KV, PAGE, hd)
+          and tuple(v_cache.shape[1:]) == (KV, PAGE, vd), "attention_pooled: cache layout")
+    _need(H % KV == 0 and 0 < vd <= 512, "attention_pooled: heads must be a multiple of kv heads, values at most 512 wide")
+    for b, name in ((sink, "sink"), (head_bias, "head_bias")):
+        _need(b is None or (b.dtype == torch.float32 and b.is_contiguous() and b.numel() == H), f"attention_pooled: {name} must be float32 [heads]")
+    _need(weights in ATTENTION_WEIGHTS, f"attention_pooled: weights {weights!r} (softmax, sigmoid)")
+    if pool:
+        _need(window > 0 and pk.dtype == pv.dtype == torch.float32 and pk.is_contiguous() and pv.is_contiguous()
+              and tuple(pk.shape[1:]) == (KV, PAGE, hd) and tuple(pv.shape[1:]) == (KV, PAGE, vd), "attention_pooled: pooled rows")
+    _check(lib("attention_pooled").kl_attention_pooled(
+        _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+        _ptr(pk), _ptr(pv), _ptr(pt), 0 if pt is None else pt.shape[1], pool, _ptr(positions), _ptr(token_slot), n_tokens, H, KV, hd,
+        ctypes.c_float(scale), int(window or 0), vd, _ptr(sink), _ptr(head_bias), ATTENTION_WEIGHTS[weights], dtype_code(q.dtype),
+        _stream()), "attention_pooled")
+
+
+def pool_blocks(k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor, pooled, step, num_kv_heads: int, head_dim: int,
+                value_dim: int) -> None:
+    """Writes the mean key and mean value (float32) of every block of ``pooled.pool`` positions whose last position is one of the
+    step's tokens, from the rows the cache holds."""
+    _cuda(k_cache, v_cache, block_table, pooled.k, pooled.v, pooled.block_table)
+    _i32(block_table, "block_table"); _i32(pooled.block_table, "pooled block_table")
+    KV, hd, vd = num_kv_heads, head_dim, value_dim
+    _need(k_cache.dtype == v_cache.dtype and k_cache.is_contiguous() and v_cache.is_contiguous() and tuple(k_cache.shape[1:]) == (KV, PAGE, hd)
+          and tuple(v_cache.shape[1:]) == (KV, PAGE, vd), "pool_blocks: cache layout")
+    _need(pooled.k.dtype == pooled.v.dtype == torch.float32 and pooled.k.is_contiguous() and pooled.v.is_contiguous()
+          and tuple(pooled.k.shape[1:]) == (KV, PAGE, hd) and tuple(pooled.v.shape[1:]) == (KV, PAGE, vd), "pool_blocks: pooled rows")
+    _check(lib("attention_pooled").kl_pool_blocks(
+        _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(pooled.k), _ptr(pooled.v), _ptr(pooled.block_table),
+        pooled.block_table.shape[1], int(pooled.pool), _ptr(step.seq_slots), _ptr(step.seq_starts), _ptr(step.seq_new), step.n_seqs,
+        step.max_new, KV, hd, vd, dtype_code(k_cache.dtype), _stream()), "pool_blocks")
+
+
 # --------------------------------------------------------------------------- grouped products
 
 GROUPED_MMA_FROM_ROWS = 32       # rows from which a batched bfloat16 product takes the tensor-core kernel
@@ -515,20 +617,21 @@ MOE_MAX_EXPERTS = 256          # equals MOE_MAX_EXPERTS in moe.cu
 
 
 def moe_route(logits: torch.Tensor, top: int, renormalise: bool = False, groups: int = 1, keep_groups: int = 1,
-              renorm_eps: float = 0.0):
+              renorm_eps: float = 0.0, bias: Optional[torch.Tensor] = None):
     """(choice int32 [tokens, top], weight float32 [tokens, top]) from float32 router logits [tokens, experts]:
     softmax over all experts, the ``top`` largest, their scores (divided by their sum + ``renorm_eps`` if ``renormalise``).
     With ``groups`` > 1 the experts form that many equal groups of neighbours, a group's score is its largest score, and
-    only experts of the ``keep_groups`` best groups can be chosen."""
-    _cuda(logits)
+    only experts of the ``keep_groups`` best groups can be chosen.  ``bias``: float32 [experts], added to the logits first."""
+    _cuda(logits, bias)
     n, E = logits.shape
+    _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == E), "moe_route: float32 bias per expert")
     _need(logits.dtype == torch.float32 and logits.stride(1) == 1, "moe_route: float32 logits")
     _need(0 < top <= E <= MOE_MAX_EXPERTS, f"moe_route: {top} of {E} experts (at most {MOE_MAX_EXPERTS})")
     choice = torch.empty((n, top), dtype=torch.int32, device=logits.device)
     weight = torch.empty((n, top), dtype=torch.float32, device=logits.device)
     _need(groups >= 1 and E % groups == 0 and 1 <= keep_groups <= groups and top <= keep_groups * (E // groups),
           f"moe_route: {groups} groups of which {keep_groups} are kept do not hold {top} of {E} experts")
-    _check(lib("moe").kl_moe_route(_ptr(logits), ctypes.c_longlong(logits.stride(0)), n, E, top, int(bool(renormalise)), int(groups),
+    _check(lib("moe").kl_moe_route(_ptr(logits), ctypes.c_longlong(logits.stride(0)), _ptr(bias), n, E, top, int(bool(renormalise)), int(groups),
                                    int(keep_groups), ctypes.c_float(renorm_eps), _ptr(choice), _ptr(weight), _stream()), "moe_route")
     return choice, weight
 
@@ -615,14 +718,17 @@ def moe_combine(results: torch.Tensor, pair_pos: torch.Tensor, weight: torch.Ten
 def latent_prepare(proj: torch.Tensor, q_col: int, kv_col: Optional[int], norm_weight: Optional[torch.Tensor], eps: float,
                    inv_freq: Optional[torch.Tensor], rot_dims: int, mscale: float, interleaved: bool, positions: torch.Tensor,
                    token_slot: torch.Tensor, block_table: Optional[torch.Tensor], cache: Optional[torch.Tensor], qfull: torch.Tensor,
-                   n_tokens: int, heads: int, dim: int, rot_dim: int, kv_rank: int) -> None:
+                   n_tokens: int, heads: int, dim: int, rot_dim: int, kv_rank: int, q: Optional[torch.Tensor] = None) -> None:
     """Per token: the normed latent and the rotated shared key part into the cache row (unless ``kv_col`` is
     None: the layer reads another layer's cache), and every head's rotated query part into the last
-    ``rot_dim`` columns of its [kv_rank + rot_dim] slice of ``qfull`` (see latent.cu)."""
-    _cuda(proj, norm_weight, inv_freq, positions, token_slot, block_table, cache, qfull)
+    ``rot_dim`` columns of its [kv_rank + rot_dim] slice of ``qfull`` (see latent.cu).  ``q``: the matrix that holds the
+    queries from column ``q_col`` on, where that is not ``proj`` (queries that came through a latent of their own)."""
+    _cuda(proj, norm_weight, inv_freq, positions, token_slot, block_table, cache, qfull, q)
+    qsrc = proj if q is None else q
+    _need(qsrc.dim() == 2 and qsrc.stride(1) == 1 and qsrc.dtype == proj.dtype and qsrc.shape[0] >= n_tokens, "latent_prepare: queries")
     _i32(positions, "positions"); _i32(token_slot, "token_slot"); _i32(block_table, "block_table")
     Dk = kv_rank + rot_dim
-    _need(proj.dim() == 2 and proj.stride(1) == 1 and q_col + heads * (dim + rot_dim) <= proj.shape[1], "latent_prepare: projections")
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and q_col + heads * (dim + rot_dim) <= qsrc.shape[1], "latent_prepare: projections")
     _need(qfull.is_contiguous() and qfull.dtype == proj.dtype and qfull.shape[0] >= n_tokens and qfull.shape[1] == heads * Dk,
           "latent_prepare: query buffer")
     if kv_col is not None:
@@ -633,7 +739,8 @@ def latent_prepare(proj: torch.Tensor, q_col: int, kv_col: Optional[int], norm_w
     _need(rot_dims == 0 or (inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dims // 2),
           "latent_prepare: one frequency per pair")
     _check(lib("latent").kl_latent_prepare(
-        _ptr(proj), ctypes.c_longlong(proj.stride(0)), q_col, -1 if kv_col is None else kv_col, _ptr(norm_weight), ctypes.c_float(eps),
+        _ptr(proj), ctypes.c_longlong(proj.stride(0)), _ptr(qsrc), ctypes.c_longlong(qsrc.stride(0)), q_col, -1 if kv_col is None else kv_col,
+        _ptr(norm_weight), ctypes.c_float(eps),
         _ptr(inv_freq), rot_dims, ctypes.c_float(mscale), int(bool(interleaved)), _ptr(positions), _ptr(token_slot),
         _ptr(block_table), 0 if block_table is None else block_table.shape[1], _ptr(cache if kv_col is not None else None), _ptr(qfull),
         n_tokens, heads, dim, rot_dim, kv_rank, dtype_code(proj.dtype), _stream()), "latent_prepare")
@@ -653,11 +760,12 @@ LATENT_KERNEL = "mma"           # "simt": the plain kernel also for bfloat16 (fo
 
 
 def latent_attention(qfull: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, step, heads: int,
-                     key_dim: int, value_dim: int, scale: float, sink: Optional[torch.Tensor] = None) -> None:
+                     key_dim: int, value_dim: int, scale: float, sink: Optional[torch.Tensor] = None, window: int = 0) -> None:
     """Causal attention of ``heads`` query heads [key_dim] over the one key head of the cache's rows, the values being
     each row's first ``value_dim`` columns; out [tokens, heads * value_dim].  bfloat16 with key and value sizes that are
-    multiples of 16 and values up to 256 wide: the tensor-core kernel (attention_latent.cu); everything else: the plain one."""
-    if (qfull.dtype == torch.bfloat16 and LATENT_KERNEL == "mma" and key_dim % 16 == 0 and value_dim % 16 == 0
+    multiples of 16 and values up to 256 wide: the tensor-core kernel (attention_latent.cu); everything else: the plain one.
+    ``window``: a token reads the keys of the last so many positions only (0: all)."""
+    if (qfull.dtype == torch.bfloat16 and LATENT_KERNEL == "mma" and not window and key_dim % 16 == 0 and value_dim % 16 == 0
             and value_dim <= 256 and 3 * 64 * (key_dim + 8) * 2 <= 220 * 1024):
         _cuda(qfull, out, cache, block_table, sink)
         _i32(block_table, "block_table")
@@ -677,7 +785,7 @@ def latent_attention(qfull: torch.Tensor, out: torch.Tensor, cache: torch.Tensor
             ctypes.c_float(scale), splits, _ptr(part), n, _stream()), "latent_attention_mma", 2 if splits > 1 else 1)
         return
     attention_simt(qfull, heads * key_dim, out, cache, cache, block_table, step.positions, step.token_slot, step.n_tokens,
-                   heads, 1, key_dim, scale, 0, value_dim=value_dim, sink=sink)
+                   heads, 1, key_dim, scale, int(window or 0), value_dim=value_dim, sink=sink)
 
 
 # --------------------------------------------------------------------------- gated linear recurrence

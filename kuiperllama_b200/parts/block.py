@@ -17,9 +17,10 @@ class PreNormBlock:
     The residual stream is float32.  A block receives the stream and a *pending* delta that
     the block before it has not added yet; every norm adds the pending delta while it reads
     the row, so no add runs as a kernel of its own.  The block returns the stream and its
-    own feed-forward output as the next pending delta."""
+    own feed-forward output as the next pending delta (the mixer's, in a layer without a
+    feed-forward)."""
 
-    def __init__(self, mixer_norm: Norm, mixer: Mixer, feed_forward_norm: Norm, feed_forward: FeedForward):
+    def __init__(self, mixer_norm: Norm, mixer: Mixer, feed_forward_norm: Optional[Norm], feed_forward: Optional[FeedForward]):
         self.mixer_norm, self.mixer = mixer_norm, mixer
         self.feed_forward_norm, self.feed_forward = feed_forward_norm, feed_forward
 
@@ -36,6 +37,11 @@ class PreNormBlock:
         n = self.mixer_norm.forward(residual, pending, step.n_tokens)
         if isinstance(n, NormedLazy) and not self.mixer.accepts_lazy_norm:
             n = n.dense()
+        if self.feed_forward is None:
+            step.residual_sink = sink_for(self.mixer, after)
+            mixed = self.mixer.forward(n, step, cache)
+            step.residual_sink = None
+            return residual, mixed
         step.residual_sink = sink_for(self.mixer, self.feed_forward_norm)
         mixed = self.mixer.forward(n, step, cache)
         n = self.feed_forward_norm.forward(residual, mixed, step.n_tokens)

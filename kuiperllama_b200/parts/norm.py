@@ -16,18 +16,21 @@ class RMSNorm(Norm):
     """out = w * x * rsqrt(mean(x^2) + eps) on x = residual + delta, statistics in 32 bits
     (ExiledOfCode/KuiperLLama rmsnorm_kernel.cu:70-106; the add is its add_kernel.cu:4-12,
     fused here).  ``size``, ``eps`` and the tensor's ``name`` come from the spec; with ``weight_offset`` c the
-    stored tensor is w - c (a weight kept around zero: the norm multiplies by c + stored)."""
+    stored tensor is w - c (a weight kept around zero: the norm multiplies by c + stored); with ``scalar`` the
+    stored tensor is ONE number (shape ()), the weight of every coordinate."""
 
     @classmethod
     def manifest(cls, spec: PartSpec, prefix: str) -> Dict[str, TensorDecl]:
         init = "normal" if spec.get("weight_offset") else "one_plus_normal"
-        return {prefix + spec["name"]: TensorDecl((spec["size"],), role="vector", init=init)}
+        return {prefix + spec["name"]: TensorDecl(() if spec.get("scalar") else (spec["size"],), role="vector", init=init)}
 
     def __init__(self, spec, prefix, tensors, runtime: Runtime):
         super().__init__(spec, prefix, tensors, runtime)
         self.size = int(spec["size"])
         self.eps = float(spec["eps"])
         self.weight = tensors[prefix + spec["name"]].to(device=runtime.device, dtype=torch.float32).contiguous()
+        if spec.get("scalar"):
+            self.weight = self.weight.reshape(1).expand(self.size).contiguous()          # the kernels read a weight per coordinate
         if spec.get("weight_offset"):
             self.weight = (self.weight + float(spec["weight_offset"])).contiguous()      # exact for a bfloat16 checkpoint: 32-bit sum
 

@@ -16,7 +16,8 @@ def rotary_inverse_frequencies(rotary_dim: int, theta: float, scaling: Optional[
 
     ``scaling`` with rope_type "llama3" rescales by wavelength 2 pi / freq: shorter than
     original / high_freq_factor unchanged; longer than original / low_freq_factor divided
-    by factor; between them interpolated linearly in original / wavelength.  KuiperLLama has
+    by factor; between them interpolated linearly in original / wavelength.  rope_type "linear" divides every
+    frequency by ``factor``; "yarn" is ``yarn_frequencies``.  KuiperLLama has
     no such rule; this follows the published meaning of those config.json keys."""
     freqs = [1.0 / (float(theta) ** ((2.0 * j) / rotary_dim)) for j in range(rotary_dim // 2)]
     if scaling is None:
@@ -26,6 +27,8 @@ def rotary_inverse_frequencies(rotary_dim: int, theta: float, scaling: Optional[
         return freqs
     if kind == "yarn":
         return yarn_frequencies(freqs, rotary_dim, float(theta), scaling)
+    if kind == "linear":                               # positions stretched by a factor: every frequency divided by it
+        return [f / float(scaling["factor"]) for f in freqs]
     if kind != "llama3":
         raise ValueError(f"unknown rope scaling {kind!r}")
     factor = float(scaling["factor"])
@@ -70,7 +73,7 @@ def rotary_magnitude(scaling: Optional[dict]) -> float:
 
 @register_position("rope")
 class RotaryPosition(PositionEncoding):
-    """Spec: ``head_dim``, ``theta``, ``scaling`` (None, a llama3 dict or a yarn dict) and optionally
+    """Spec: ``head_dim``, ``theta``, ``scaling`` (None, a llama3 dict, a yarn dict or a linear dict) and optionally
     ``rotary_dim`` (default: the whole head) and ``pairing`` ("half": element i with i + rotary_dim / 2, the
     default; "interleaved": element 2i with 2i + 1).  The rotation itself happens in the mixer's kernels;
     this part owns the frequencies, the factor on cos and sin (``magnitude``) and the pairing."""
