@@ -86,7 +86,9 @@ def register_cache_kind(name: str):
     built as ``cls(request, entries, max_tokens_pages, n_slots, blocks_per_seq, dtype, device,
     window_step_tokens)`` for the schedule entries whose requests are equal, and offers
 
-    * ``reserve(slot, old_length, new_length)``: room for the sequence to grow (raises CacheError),
+    * ``reserve(slot, old_length, new_length)``: room for the sequence to grow (raises CacheError); optionally
+      ``grows_at(old_length) -> bool``: whether one more token needs new storage (asked before a step of single tokens;
+      without it ``reserve`` is called at every page border),
     * ``release(slot)``: everything the sequence holds goes back,
     * ``flush()``: bring device-side tables up to date on the current stream,
     * ``view(j) -> (k, v, block_table)`` or ``(k, v, block_table, pooled)``: what execution ``entries[j]`` sees,
@@ -165,6 +167,11 @@ class PagedGroup:
         """The first position a step that starts at ``old_length``, or a later one, still reads (with a window)."""
         return max(0, old_length - self.request.window + 1)
 
+    def grows_at(self, old_length: int) -> bool:
+        """Whether a sequence of ``old_length`` tokens needs new storage for one more token (so that a step of single tokens
+        may skip ``reserve`` where it does not)."""
+        return old_length % PAGE == 0
+
     def window_tokens(self) -> int:
         """Tokens before a step's first that the group keeps per sequence (with a window)."""
         return self.request.window
@@ -238,6 +245,11 @@ class PooledWindowGroup(PagedGroup):
 
     def window_tokens(self) -> int:
         return self.request.window + self.request.pool
+
+    def grows_at(self, old_length: int) -> bool:
+        # a new page of keys, or the token completes the block whose row of means is the first of a new page
+        P = self.request.pool
+        return old_length % PAGE == 0 or ((old_length + 1) % P == 0 and ((old_length + 1) // P - 1) % PAGE == 0)
 
     def reserve(self, slot: int, old_length: int, new_length: int) -> None:
         super().reserve(slot, old_length, new_length)
@@ -348,6 +360,12 @@ class SequenceCache:
             raise CacheError(f"a step of {new_length - self.lengths[slot]} tokens exceeds the promised {self.window_step_tokens}")
         for g in self.groups:
             g.reserve(slot, self.lengths[slot], new_length)
+
+    def grows_at(self, slot: int) -> bool:
+        """Whether the sequence in ``slot`` needs ``reserve`` before it takes one more token: some group wants new storage
+        for it (a group that does not say is asked at every page border)."""
+        n = self.lengths[slot]
+        return any(g.grows_at(n) if hasattr(g, "grows_at") else n % PAGE == 0 for g in self.groups)
 
     def flush_tables(self) -> None:
         """Bring the device's block tables up to date (copies on the current stream)."""

@@ -337,7 +337,7 @@ class Engine:
             if not cache.slots.is_held(s):
                 raise StepError(f"slot {s} is not held by a sequence")
             st = lengths[s]
-            if st % PAGE == 0 or st + 1 > cache.max_seq_len:      # a new page, or the limit: let the cache decide
+            if cache.grows_at(s) or st + 1 > cache.max_seq_len:   # new storage (a page), or the limit: let the cache decide
                 try:
                     cache.reserve(s, st + 1)
                 except CacheError as e:

@@ -117,20 +117,17 @@ def attention_pooled_sigmoid(h: torch.Tensor, m: dict, w: Dict[str, torch.Tensor
     v = k                                              # the keys as projected
     q, k = rms_norm(q, w["q.norm"], eps), rms_norm(k, w["k.norm"], eps)
     rep = H // G
-    out = torch.zeros(n, H, d, dtype=F)
-    kb, vb = pooled_blocks(k, P), pooled_blocks(v, P)
-    for i in range(n):
-        for hh in range(H):
-            g = hh // rep
-            acc = torch.zeros(d, dtype=F)
-            for b in range(kb.shape[0]):
-                if b * P + P - 1 <= i - W:
-                    s = (q[i, hh] @ kb[b, g]) * m["scale"] + w["pb"][hh]
-                    acc += torch.sigmoid(s) * vb[b, g]
-            lo = max(0, i - W + 1)
-            s = (k[lo:i + 1, g] @ q[i, hh]) * m["scale"] + w["pb"][hh]
-            acc += torch.sigmoid(s) @ v[lo:i + 1, g]
-            out[i, hh] = acc
+    kb, vb = pooled_blocks(k, P), pooled_blocks(v, P)                       # the means of the normed keys, and of the values
+    k, v, kb, vb = (t.repeat_interleave(rep, dim=1) for t in (k, v, kb, vb))
+    bias = w["pb"][:, None, None]
+    seen = window_mask(n, W)
+    weight = torch.sigmoid(torch.einsum("ihd,jhd->hij", q, k) * m["scale"] + bias) * seen[None]
+    out = torch.einsum("hij,jhd->ihd", weight, v)
+    if kb.shape[0]:
+        last = torch.arange(kb.shape[0])[None, :] * P + P - 1               # a block's last position
+        whole = last <= torch.arange(n)[:, None] - W                        # the block lies wholly before the window
+        weight = torch.sigmoid(torch.einsum("ihd,bhd->hib", q, kb) * m["scale"] + bias) * whole[None]
+        out = out + torch.einsum("hib,bhd->ihd", weight, vb)
     return out.reshape(n, H * d) @ w["o"].T
 
 
@@ -164,8 +161,19 @@ def route(h: torch.Tensor, router: torch.Tensor, bias: torch.Tensor, top: int) -
     return idx, torch.softmax(val, dim=-1)
 
 
-def moe(h: torch.Tensor, mlp: dict, w: Dict[str, torch.Tensor]) -> torch.Tensor:
+def route_margin(h: torch.Tensor, router: torch.Tensor, bias: torch.Tensor, top: int) -> torch.Tensor:
+    """[n]: how far the last chosen logit lies above the first one left out, in units of the row's spread (inf: all chosen)."""
+    z = h @ router.T + bias
+    if z.shape[-1] <= top:
+        return torch.full((h.shape[0],), math.inf, dtype=F)
+    val = torch.sort(z, dim=-1, descending=True).values
+    return (val[:, top - 1] - val[:, top]) / z.std(dim=-1).clamp_min(1e-30)
+
+
+def moe(h: torch.Tensor, mlp: dict, w: Dict[str, torch.Tensor], margins: Optional[list] = None) -> torch.Tensor:
     choice, weight = route(h, w["router"], w["router.b"], mlp["router"]["top"])
+    if margins is not None:
+        margins.append(route_margin(h, w["router"], w["router.b"], mlp["router"]["top"]))
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for c, p in zip(choice[t].tolist(), weight[t]):
@@ -182,8 +190,8 @@ def sub(weights: Dict[str, torch.Tensor], prefix: str) -> Dict[str, torch.Tensor
     return {k[len(prefix):]: v.to(F) for k, v in weights.items() if k.startswith(prefix)}
 
 
-def forward(config: dict, weights: Dict[str, torch.Tensor], tokens: List[int]) -> Tuple[torch.Tensor, List[torch.Tensor]]:
-    """(logits [n, vocab], the stream after every layer) of one whole sequence."""
+def forward(config: dict, weights: Dict[str, torch.Tensor], tokens: List[int], margins: Optional[list] = None) -> Tuple[torch.Tensor, List[torch.Tensor]]:
+    """(logits [n, vocab], the stream after every layer) of one whole sequence.  ``margins`` collects every router's ``route_margin``."""
     eps = float(config["norm"]["eps"])
     x = weights["embed"].to(F)[torch.tensor(tokens, dtype=torch.long)]
     streams = []
@@ -193,7 +201,7 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens: List[int]) -
         x = x + MIXERS[layer["type"]](h, layer["mixer"], sub(weights, p + "mix."), eps)
         if layer.get("mlp") is not None:
             h = scalar_rms_norm(x, weights[p + "norm2"].to(F), eps)
-            x = x + moe(h, layer["mlp"], sub(weights, p + "mlp."))
+            x = x + moe(h, layer["mlp"], sub(weights, p + "mlp."), margins)
         streams.append(x)
     x = scalar_rms_norm(x, weights["final.norm"].to(F), eps)
     return x @ weights["head"].to(F).T, streams
