@@ -4,7 +4,8 @@ B200, and the two other workloads of the same family (Llama-2-7B shape with ragg
 Llama-3.2-1B shape with temperature sampling).
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B] [--impl reference] [--no-points]
-    python bench.py --compare terolix|munadra|bededra [--sizes 1b,8b-8-layers]      (another design beside Llama; see compare_designs)
+    python bench.py --compare terolix|munadra|bededra|dofevik [--sizes 1b,8b-8-layers]   (another design beside Llama, Dofevik beside
+                                                                                         Munadra, the closest model; see compare_designs)
 
 A "step" is one decode step of a batch (default 8 sequences that each hold a 512-token
 prompt, context limit 4096).  One JSON line is printed:
@@ -411,6 +412,26 @@ def bededra_config(width, layers, heads, kv_heads, head_dim, vocab):
             "layers": [order[i % 4] for i in range(layers)]}
 
 
+def dofevik_config(width, layers, heads, kv_heads, head_dim, vocab):
+    """A Dofevik model of ``layers`` layers in groups of four: latent attention (queries through a latent of 768, a latent of 256
+    for keys and values, heads of ``head_dim`` unrotated and half as many rotated dimensions), grouped-query attention with a sink
+    (the Llama shape's heads, half of every head rotated), attention with sigmoid weights whose values are its keys (blocks of 64
+    positions pooled before the window), and latent attention again; every window 1,024 keys; every layer with 16 squared-relu
+    experts of a quarter of the Llama shape's intermediate size of which a token uses 4, and a shared expert of that size."""
+    inter = COMPARE_INTER[width]
+    lat = {"type": "latent_attention", "mixer": {"heads": heads, "dim": head_dim, "rot_dim": head_dim // 2, "vdim": head_dim, "kv_rank": 256,
+                                                 "q_rank": 768, "scale": (1.5 * head_dim) ** -0.5, "mask": {"size": 1024},
+                                                 "rot": {"base": 500000.0, "dims": head_dim // 2}}}
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
+                                          "mask": {"size": 1024}, "rot": {"base": 500000.0, "dims": head_dim // 2, "scaling": {"factor": 8.0}}}}
+    att2 = {"type": "attention_2", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5,
+                                             "mask": {"size": 1024, "pool": 64}}}
+    moe = {"kind": "moe", "router": {"experts": 16, "top": 4}, "expert": {"ff": inter // 4}, "shared": {"ff": inter // 4}}
+    order = [lat, att, att2, lat]
+    return {"architecture": "Dofevik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "layers": [dict(order[i % 4], mlp=moe) for i in range(layers)]}
+
+
 COMPARE_INTER = {2048: 8192, 4096: 14336}
 
 
@@ -448,15 +469,22 @@ def compare_designs(args):
             other = bededra_config(z["width"], z["layers"], z["heads"], z["kv_heads"], z["head_dim"], vocab)
         else:
             other = terolix_config(z["width"], z["layers"], z["heads"], z["kv_heads"], z["head_dim"], z["ff"], vocab)
+        base = "llama"
+        if args.compare == "dofevik":                     # beside the closest existing model: latent attention and experts
+            base, llama = "munadra", munadra_config(z["width"], z["layers"], z["heads"], z["head_dim"], vocab)
+            other = dofevik_config(z["width"], z["layers"], z["heads"], z["kv_heads"], z["head_dim"], vocab)
         out[name] = {}
-        for design, cfg in (("llama", llama), (args.compare, other)):
+        for design, cfg in ((base, llama), (args.compare, other)):
             model = kl.random_model(config_from_dict(cfg), seed=0, dtype="bfloat16", device="cuda:0")
             infer = kl.Inference(model, max_tokens=64 * CONTEXT, max_batch=64, max_seq_len=CONTEXT)
             wbytes = model.weight_bytes()
             matrix_params = wbytes / 2 - vocab * z["width"]
-            if design in ("munadra", "bededra"):          # a token uses 4 of a layer's 16 experts: count what it multiplies by
+            if design in ("munadra", "bededra", "dofevik"):       # a token uses 4 of a layer's 16 experts: count what it multiplies by
                 moe_layers = sum(1 for l in cfg["layers"] if l["mlp"] and l["mlp"]["kind"] == "moe")
-                matrix_params -= moe_layers * 12 * 3 * z["width"] * (COMPARE_INTER[z["width"]] // 4)
+                per_expert = (2 if design == "dofevik" else 3) * z["width"] * (COMPARE_INTER[z["width"]] // 4)   # no gate: two matrices
+                matrix_params -= moe_layers * 12 * per_expert
+            if design == "dofevik":
+                matrix_params -= vocab * z["width"]           # a classifier of its own, which runs on the wanted rows only
             t = time_prefill(infer, warmup=3, repeats=5, seed=2, checks=checks)
             r = {"weight_gb": round(wbytes / 1e9, 3), "prefill_tokens_per_s": round(PREFILL_LEN / t, 1), "prefill_ms": round(t * 1e3, 3),
                  "prefill_tc_frac": round(2 * PREFILL_LEN * matrix_params / t / (pk["bf16_tflops"] * 1e12), 4)}
@@ -470,9 +498,9 @@ def compare_designs(args):
             out[name][design] = r
             del infer, model
             torch.cuda.empty_cache()
-        a, b = out[name][args.compare], out[name]["llama"]
-        out[name][args.compare + "_over_llama"] = {k: round(a[k] / b[k], 3) for k in a if k.endswith("tokens_per_s")}
-    print(json.dumps({"metric": f"prefill and decode tok/s of {args.compare.capitalize()} beside Llama at equal size, bf16, random weights",
+        a, b = out[name][args.compare], out[name][base]
+        out[name][args.compare + "_over_" + base] = {k: round(a[k] / b[k], 3) for k in a if k.endswith("tokens_per_s")}
+    print(json.dumps({"metric": f"prefill and decode tok/s of {args.compare.capitalize()} beside {base.capitalize()} at equal size, bf16, random weights",
                       "impl": "ours", "n_gpus": 1, "dtype": "bf16", "data": "synthetic: random weights N(0, 0.02), uniform random token ids",
                       "prompt_len": PROMPT_LEN, "prefill_len": PREFILL_LEN, "peaks": pk["source"], "sizes": out,
                       "clocks": clocks.stop(), "checks": checks}))
@@ -504,8 +532,8 @@ def main():
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--no-points", action="store_true",
                     help="only the headline: skip the prefill, the batch 1, 64 and 128 points and the two other workloads")
-    ap.add_argument("--compare", default=None, choices=["terolix", "munadra", "bededra"],
-                    help="instead of the default workload: this design beside Llama at equal size (prefill and decode rates)")
+    ap.add_argument("--compare", default=None, choices=["terolix", "munadra", "bededra", "dofevik"],
+                    help="instead of the default workload: this design beside Llama (Dofevik: beside Munadra) at equal size (prefill and decode rates)")
     ap.add_argument("--sizes", default="", help="with --compare: which of the sizes to run, with commas (default: all)")
     args = ap.parse_args()
     if args.impl == "reference":

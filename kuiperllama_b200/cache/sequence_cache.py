@@ -11,7 +11,7 @@ execution of a layer that asks for them, and fixed-size state per slot.
   the window still touches: before a step, the pages of a sequence that lie wholly below
   ``length - window + 1`` go back to the group's pool (no query of this or a later step reads
   them), so such a group can be given a smaller pool (``window_step_tokens``).
-* A group of kind "pooled" keeps, beside the window's pages, one float32 row per kv head for every complete
+* A group of kind "pooled" keeps, beside the window's pages, one row per kv head for every complete
   block of ``pool`` positions (the mean of the block's keys, and of its values) in pages of a second pool;
   those rows stay as long as the sequence lives.
 * Beside the pages every execution may ask for per-slot state of a fixed shape (a
@@ -72,8 +72,8 @@ class CacheView:
 @dataclass
 class PooledView:
     """Rows of block means: row b of a sequence lies in page ``block_table[slot, b // PAGE]`` at place b % PAGE."""
-    k: torch.Tensor                       # float32 [pages, kv_heads, PAGE, head_dim]
-    v: torch.Tensor                       # float32 [pages, kv_heads, PAGE, value_dim]
+    k: torch.Tensor                       # [pages, kv_heads, PAGE, head_dim], the cache's dtype
+    v: torch.Tensor                       # [pages, kv_heads, PAGE, value_dim]
     block_table: torch.Tensor             # int32 [slots, blocks_per_seq]
     pool: int                             # positions per block
 
@@ -214,7 +214,7 @@ class KeysOnlyGroup(PagedGroup):
 @register_cache_kind("pooled")
 class PooledWindowGroup(PagedGroup):
     """A window of keys and values in pages, as ``PagedGroup`` keeps them, and beside it the means of whole blocks:
-    for every complete block of ``request.pool`` positions one float32 key row and one float32 value row per kv head
+    for every complete block of ``request.pool`` positions one key row and one value row per kv head, in the cache's dtype
     (written by the mixer's kernel when the block's last position arrives), in pages of ``PAGE`` rows from a second
     pool with a block table of its own.  A block's positions stay in the window's pages until the block is complete,
     also where the window is shorter than a block; the means stay until the sequence ends."""
@@ -232,8 +232,8 @@ class PooledWindowGroup(PagedGroup):
         n_pool_pages = max(1, min(n_slots * self.pool_blocks_per_seq, pages_for(n_pages * PAGE // P, PAGE) + n_slots))
         self.pool_pages = FreeList(n_pool_pages, "page of block means")
         shape = (len(entries), n_pool_pages, request.kv_heads, PAGE)
-        self.pool_k = torch.zeros(shape + (request.head_dim,), dtype=torch.float32, device=device)
-        self.pool_v = torch.zeros(shape + (request.value_dim or request.head_dim,), dtype=torch.float32, device=device)
+        self.pool_k = torch.zeros(shape + (request.head_dim,), dtype=dtype, device=device)
+        self.pool_v = torch.zeros(shape + (request.value_dim or request.head_dim,), dtype=dtype, device=device)
         self.pool_table_host = torch.zeros((n_slots, self.pool_blocks_per_seq), dtype=torch.int32)
         self.pool_table = torch.zeros((n_slots, self.pool_blocks_per_seq), dtype=torch.int32, device=device)
         self.pool_slot_pages: List[List[int]] = [[] for _ in range(n_slots)]
@@ -278,7 +278,7 @@ class PooledWindowGroup(PagedGroup):
         return self.k[j], self.v[j], self.table, PooledView(self.pool_k[j], self.pool_v[j], self.pool_table, self.request.pool)
 
     def bytes(self) -> int:
-        return super().bytes() + 4 * (self.pool_k.numel() + self.pool_v.numel())
+        return super().bytes() + self.pool_k.element_size() * (self.pool_k.numel() + self.pool_v.numel())
 
 
 class SequenceCache:

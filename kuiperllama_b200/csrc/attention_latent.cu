@@ -9,7 +9,8 @@
 // exp2), P as the A operand straight from the accumulators, O += P V with V = the same page's first Dv
 // columns read through ldmatrix.trans.  O stays in registers (16 x Dv per warp), so Dv <= 256 here; wider
 // latents and float32 take the plain kernel (attention_simt.cu).  A sink per head joins the denominator at
-// the end.  In a decode step a sequence's pages are cut over several CTAs (split-KV) whose pieces a small kernel
+// the end.  With a window a row sees the keys of its last `window` positions only, and a CTA starts at the page of its
+// first token's first key.  In a decode step a sequence's pages are cut over several CTAs (split-KV) whose pieces a small kernel
 // merges, so that few sequences still fill the machine.  Rows of shared memory are Dk + 8 elements apart, which keeps the eight rows of an ldmatrix on
 // different banks when Dk is a multiple of 16.
 //
@@ -57,7 +58,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
                             const int* __restrict__ block_table, int blocks_per_seq, const int* __restrict__ cu_tokens,
                             const int* __restrict__ seq_slots, const int* __restrict__ seq_starts, const int* __restrict__ seq_new,
                             const float* __restrict__ sink, int H, int HB, int TT, int Dk, int Dv, float scale_log2,
-                            int splits, float* __restrict__ part, int stages) {
+                            int splits, float* __restrict__ part, int stages, int window) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -74,9 +75,11 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
     const int* table = block_table + (size_t)slot * blocks_per_seq;
     const int tokens_here = min(TT, n_new - t0);
     // this CTA's pages: all of them, or (splits > 1, a decode step) one of `splits` runs of pages
+    // (with a window: from the page that holds the first key the tile's first token still sees)
     const int all_pages = (start + t0 + tokens_here - 1) / PAGE + 1;
-    const int per = (all_pages + splits - 1) / splits;
-    const int first_page = piece * per, last_page = min(all_pages, first_page + per) - 1;
+    const int low_page = window > 0 ? max(0, start + t0 - window + 1) / PAGE : 0;
+    const int per = (all_pages - low_page + splits - 1) / splits;
+    const int first_page = low_page + piece * per, last_page = min(all_pages, first_page + per) - 1;
 
     auto load_page = [&](int j, int buf) {
         const bf16* src = cache + (size_t)table[j] * PAGE * Dk;
@@ -99,13 +102,14 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
 
     // this thread's two rows of the warp's 16: g and g + 8
     const int g = lane >> 2, quad = lane & 3;
-    int pos[2];
+    int pos[2], lo[2];
     bool live[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int r = warp * 16 + g + 8 * i, tt = r / HB;
         live[i] = tt < tokens_here && h0 + r % HB < H;
         pos[i] = live[i] ? start + t0 + tt : -1;
+        lo[i] = window > 0 ? max(0, pos[i] - window + 1) : 0;          // the first key the row sees
     }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     float o[NVT][4];
@@ -155,7 +159,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int key = key0 + n * 8 + (c & 1);
-                const float v = key <= pos[c >> 1] ? sc[n][c] * scale_log2 : -INFINITY;
+                const float v = (key <= pos[c >> 1] && key >= lo[c >> 1]) ? sc[n][c] * scale_log2 : -INFINITY;
                 sc[n][c] = v;
                 mx[c >> 1] = fmaxf(mx[c >> 1], v);
             }
@@ -277,13 +281,13 @@ static bool latent_two_buffers() {
 using namespace kl;
 
 // q: [tokens, H, Dk], out: [tokens, H, Dv], cache: [pages, 1, 64, Dk], all bfloat16; Dk % 16 == 0, Dv % 16 == 0, Dv <= 256
-// and <= Dk.  scale multiplies the dot products; sink: float32 [H] or null.  max_new: the most tokens a sequence brings.
+// and <= Dk.  scale multiplies the dot products; sink: float32 [H] or null; window: keys a token sees (0: all).  max_new: the most tokens a sequence brings.
 // splits > 1 (a decode step: one token per sequence): every sequence's pages are cut into that many runs, each a CTA that
 // leaves its sums in part (float32 [n_tokens * H][splits][Dv + 2]), and a second kernel puts the pieces together.
 KL_API int kl_latent_attention_mma(const void* q, void* out, const void* cache, const int* block_table, int blocks_per_seq,
                                    const int* cu_tokens, const int* seq_slots, const int* seq_starts, const int* seq_new, int n_seqs,
                                    int max_new, const float* sink, int H, int Dk, int Dv, float scale, int splits, float* part,
-                                   int n_tokens, cudaStream_t stream) {
+                                   int n_tokens, int window, cudaStream_t stream) {
     if (n_seqs <= 0 || max_new <= 0) return KL_OK;
     if (splits < 1 || splits > 32 || (splits > 1 && (part == nullptr || max_new != 1 || Dv % 2))) return KL_ERR_BAD_SIZE;
     if (H <= 0 || Dk % 16 || Dv % 16 || Dv <= 0 || Dv > 256 || Dv > Dk) return KL_ERR_BAD_SIZE;
@@ -306,7 +310,7 @@ KL_API int kl_latent_attention_mma(const void* q, void* out, const void* cache, 
         }                                                                                                                     \
         launch_kernel(latent_attention_mma_kernel<NVT>, grid, LA_THREADS, smem, stream, (const bf16*)q, (bf16*)out,           \
                       (const bf16*)cache, block_table, blocks_per_seq, cu_tokens, seq_slots, seq_starts, seq_new, sink, H, HB, TT, \
-                      Dk, Dv, scale_log2, splits, part, stages);                                                              \
+                      Dk, Dv, scale_log2, splits, part, stages, window);                                                      \
     } while (0)
     if (Dv <= 64) KL_LA(8);
     else if (Dv <= 128) KL_LA(16);

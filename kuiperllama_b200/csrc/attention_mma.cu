@@ -21,6 +21,13 @@
 // on whole pages (two stages, three CTAs per SM; or three stages, two per SM) and as light CTAs
 // of two warps on half pages (three stages of 16 KB at a head size of 128: four CTAs per SM),
 // taken where three per SM would leave CTAs for a second round.
+//
+// Options beyond that (`AttentionExtra`, all off for the Llama decoder): a sink per head in the softmax's
+// denominator (exp(sink[h]): no key, no value); WEIGHTS = 1: the weight of a visible key is
+// sigmoid(score + head_bias[h]), not normalised over the keys; and pooled rows: a second paged cache
+// whose row b holds the mean key and mean value of the positions b * pool .. (b + 1) * pool - 1 and is
+// seen by position p when the whole block lies before p's window, (b + 1) * pool - 1 <= p - window.  The
+// pooled rows are walked first, as units of their own (by the CTA of split 0), then the window's keys.
 #include "common.cuh"
 
 namespace kl {
@@ -53,6 +60,19 @@ __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+// 1 / x by the special-function unit (1 / inf = 0, so a masked key's sigmoid weight is exactly 0)
+__device__ __forceinline__ float fast_rcp(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// What a softmax's sum and output are multiplied by, and what joins the sum, when a sink (exp2 domain) joins the denominator
+// of a row whose running maximum is M: the row is rescaled to max(M, sink).
+__device__ __forceinline__ void sink_terms(float M, float sink2, float& keep, float& add) {
+    const float Ms = fmaxf(M, sink2);
+    keep = M == -INFINITY ? 0.f : exp2f(M - Ms);
+    add = exp2f(sink2 - Ms);
 }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -100,6 +120,17 @@ struct DecodeFuse {
     bf16* k_cache_w;              // the cache, writable
     bf16* v_cache_w;
     int* counters;                // [rows * KV], zero
+};
+
+// What only some mixers ask for (all null / 0: plain causal softmax attention).
+struct AttentionExtra {
+    const float* sink;            // float32 [H]: exp(sink[h]) joins head h's softmax denominator
+    const float* head_bias;       // float32 [H]: sigmoid weights add it to the score
+    const bf16* pool_k;           // [pages][KV][PAGE][HD]: rows of block means (keys), or null
+    const bf16* pool_v;           // the same for values
+    const int* pool_table;        // [slots][pool_blocks_per_seq]
+    int pool_blocks_per_seq;
+    int pool;                     // positions per block; 0: no pooled rows
 };
 
 // The decode step's token of one sequence, for one kv group: its q (the group's G heads) into q_sm
@@ -219,7 +250,7 @@ __device__ __forceinline__ void make_token_qkv(const DecodeFuse& fuse, bf16* q_s
 // SK: keys per stage, a cache page (64) or half of one.  Half pages with two warps make a CTA of the
 // decode layout light enough (48 KB of stages at a head size of 128) for four of them on an SM, or
 // with two stages (32 KB) for six.
-template <int HD, int WM, int WN, int NS, int SK>
+template <int HD, int WM, int WN, int NS, int SK, int WEIGHTS>
 __global__ void __launch_bounds__(32 * WM * WN, SK < PAGE ? (NS == 2 ? 6 : 4) : (NS == 2 ? ((HD == 64 && WN > 1) ? 4 : 3) : 2))   // half pages: six CTAs of two stages or four of three; whole pages, NS = 2: three CTAs per SM (168 registers, 3 x 64 KB of stages), four in the decode layout with a head size of 64
 attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                      const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
@@ -227,7 +258,7 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
                      const int* __restrict__ cu_tokens, const int* __restrict__ seq_slots,
                      const int* __restrict__ seq_starts, const int* __restrict__ seq_new,
                      float* __restrict__ part_o, float* __restrict__ part_ml,
-                     int H, int KV, int Gp, float scale_log2, int window, int S, DecodeFuse fuse) {
+                     int H, int KV, int Gp, float scale_log2, int window, int S, DecodeFuse fuse, AttentionExtra ex) {
     pdl_launch_dependents();
     // The fused decode form reads only what earlier steps left (the batch's index arrays, the
     // block table, old cache pages) until it has requested its first page; then it waits.
@@ -259,7 +290,8 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
     const int quad = lane >> 2, tq = lane & 3;
 
     // this thread's two rows (quad and quad + 8 of the warp's 16)
-    int tok[2], head[2], pos[2], lo[2];
+    int tok[2], head[2], pos[2], lo[2], nb[2];
+    float hbias[2];                                      // sigmoid weights: the head's number, in the exp2 domain
     bool valid[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -270,6 +302,8 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
         head[i] = g * G + hh;
         pos[i] = valid[i] ? start + tl : -1;
         lo[i] = (window > 0 && valid[i]) ? max(0, pos[i] - window + 1) : 0;
+        nb[i] = (ex.pool > 0 && valid[i]) ? lo[i] / ex.pool : 0;                  // pooled rows this row sees: blocks wholly before its window
+        hbias[i] = (WEIGHTS == 1 && ex.head_bias != nullptr && valid[i]) ? ex.head_bias[head[i]] * 1.4426950408889634f : 0.f;
     }
     // pages this CTA reads
     const int last_tok = min(T, t0 + BT) - 1;
@@ -280,20 +314,33 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
     const int p_begin = first_page + z * per, p_end = min(first_page + n_pages, p_begin + per);
     const int* table = block_table + (size_t)slot * blocks_per_seq;
     const int full_below = start + t0;                   // keys <= this are visible to every valid row (no window)
+    // Pooled rows: the first PU units of the walk, taken by the CTA of split 0.
+    const int max_nb = ex.pool > 0 ? max(0, max_pos - window + 1) / ex.pool : 0;
+    const int PU = (ex.pool > 0 && z == 0) ? (max_nb + SK - 1) / SK : 0;
+    const int* ptable = ex.pool > 0 ? ex.pool_table + (size_t)slot * ex.pool_blocks_per_seq : nullptr;
 
     // Units of SK keys this CTA reads: its pages, without what lies wholly behind the last position.
     const int u_begin = p_begin * UPP, u_end = min(p_end * UPP, max_pos / SK + 1);
+    // `unit` counts from u_begin - PU: the pooled units come first (their index below u_begin), then the keys' units.
     auto issue = [&](int unit, int st) {
-        const size_t off = (((size_t)table[unit / UPP] * KV + g) * PAGE + (unit % UPP) * SK) * HD;
-        load_keys<HD, THREADS, SK>(k_stage + st * SK * HD, k_cache + off);
-        load_keys<HD, THREADS, SK>(v_stage + st * SK * HD, v_cache + off);
+        if (unit < u_begin) {
+            const int pu = unit - (u_begin - PU);
+            const size_t off = (((size_t)ptable[pu / UPP] * KV + g) * PAGE + (pu % UPP) * SK) * HD;
+            load_keys<HD, THREADS, SK>(k_stage + st * SK * HD, ex.pool_k + off);
+            load_keys<HD, THREADS, SK>(v_stage + st * SK * HD, ex.pool_v + off);
+        } else {
+            const size_t off = (((size_t)table[unit / UPP] * KV + g) * PAGE + (unit % UPP) * SK) * HD;
+            load_keys<HD, THREADS, SK>(k_stage + st * SK * HD, k_cache + off);
+            load_keys<HD, THREADS, SK>(v_stage + st * SK * HD, v_cache + off);
+        }
         cp_async_commit();
     };
+    const int w_begin = u_begin - PU;                    // the walk's first unit
     const bool writes_token = fuse.enabled && p_begin < p_end && p_end == first_page + n_pages;
     // Units are requested NS - 1 ahead, one cp.async group per unit in key order.  The fused
     // decode form requests what it can before it waits for the kernel before it: every unit but
     // the one this CTA is about to write the new token into.
-    int next = u_begin, groups = 0;
+    int next = w_begin, groups = 0;
     // The fused form's rotation: cos and sin of the token's position times every frequency, made once per
     // CTA before the wait (position and frequencies are known by then), so that the rotation of q and k
     // costs no sincosf on the path between the kernel ahead and the first page (it took 0.9 us of 7.6 at 8
@@ -302,7 +349,7 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
     __shared__ __align__(16) float rot_sn[HD / 2];
     if (fuse.enabled) {
         const int limit = writes_token ? max_pos / SK : u_end;
-        while (groups < NS - 1 && next < limit) { issue(next, (next - u_begin) % NS); ++next; ++groups; }
+        while (groups < NS - 1 && next < limit) { issue(next, (next - w_begin) % NS); ++next; ++groups; }
         for (int f = threadIdx.x; f < HD / 2; f += THREADS) sincosf((float)(start + t0) * fuse.inv_freq[f], &rot_sn[f], &rot_cs[f]);
         pdl_wait();
         __syncthreads();
@@ -352,21 +399,22 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
     while (groups < NS - 1) {
-        if (next < u_end) { issue(next, (next - u_begin) % NS); ++next; } else cp_async_commit();
+        if (next < u_end) { issue(next, (next - w_begin) % NS); ++next; } else cp_async_commit();
         ++groups;
     }
-    for (int pi = u_begin; pi < u_end; ++pi) {
-        const int st = (pi - u_begin) % NS;
-        if (next < u_end) { issue(next, (next - u_begin) % NS); ++next; } else cp_async_commit();
+    for (int pi = w_begin; pi < u_end; ++pi) {
+        const int st = (pi - w_begin) % NS;
+        const bool pooled = pi < u_begin;                // a unit of block means: row index = block index
+        if (next < u_end) { issue(next, (next - w_begin) % NS); ++next; } else cp_async_commit();
         cp_async_wait<NS - 1>();                         // all but the NS - 1 newest groups: unit pi has landed
         __syncthreads();
         const bf16* ks_ = k_stage + st * SK * HD;
         const bf16* vs_ = v_stage + st * SK * HD;
-        const int key0 = pi * SK + warp_n * KPW;         // first key of this warp's share
+        const int key0 = (pooled ? pi - w_begin : pi) * SK + warp_n * KPW;         // first key (or pooled row) of this warp's share
         float s[NT][4];
 #pragma unroll
         for (int n = 0; n < NT; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
-        if (key0 <= max_pos) {                           // the warp's keys are not all in the future
+        if (pooled ? key0 < max_nb : key0 <= max_pos) {  // the warp's keys are not all in the future
 #pragma unroll
             for (int ks = 0; ks < KS; ++ks) {
 #pragma unroll
@@ -380,7 +428,7 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
                 }
             }
             // scale, mask, online softmax
-            const bool need_mask = key0 + KPW - 1 > full_below || window > 0 || !valid[0] || !valid[1];
+            const bool need_mask = pooled || key0 + KPW - 1 > full_below || window > 0 || !valid[0] || !valid[1];
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
@@ -390,12 +438,20 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
                     float v = s[n][c] * scale_log2;
                     if (need_mask) {
                         const int kp = key0 + n * 8 + 2 * tq + (c & 1);
-                        if (kp > pos[i] || kp < lo[i]) v = -INFINITY;
+                        if (pooled ? kp >= nb[i] : (kp > pos[i] || kp < lo[i])) v = -INFINITY;
                     }
                     s[n][c] = v;
                     mx[i] = fmaxf(mx[i], v);
                 }
             }
+            if constexpr (WEIGHTS == 1) {
+                // sigmoid(score + bias) = 1 / (1 + 2^-(s + b)) with s and b in the exp2 domain; a masked key (-inf) weighs 0
+#pragma unroll
+                for (int n = 0; n < NT; ++n) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) s[n][c] = fast_rcp(1.f + fast_exp2(-(s[n][c] + hbias[c >> 1])));
+                }
+            } else {
             float corr[2], muse[2];
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
@@ -419,6 +475,7 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
                     s[n][c] = p;
                     l[c >> 1] += p;
                 }
+            }
             }
             // probabilities as A fragments, times the values
 #pragma unroll
@@ -475,14 +532,19 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
 #pragma unroll
             for (int w = 0; w < WN; ++w) {
                 const float mw = sm_m[w * ROWS + r];
-                const float c = mw == -INFINITY ? 0.f : exp2f(mw - M);
+                const float c = WEIGHTS == 1 ? 1.f : (mw == -INFINITY ? 0.f : exp2f(mw - M));     // sigmoid weights: the warps' sums add up
                 L += sm_l[w * ROWS + r] * c;
                 const float4 v = *reinterpret_cast<const float4*>(sm_o + ((size_t)w * ROWS + r) * OS + d);
                 acc.x += v.x * c; acc.y += v.y * c; acc.z += v.z * c; acc.w += v.w * c;
             }
             const size_t orow = (size_t)(row0 + tl) * H + (g * G + hh);
             if (S == 1) {
-                const float inv = 1.f / L;
+                float inv = 1.f;
+                if constexpr (WEIGHTS == 0) {
+                    float keep = 1.f, add = 0.f;
+                    if (ex.sink != nullptr) sink_terms(M, ex.sink[g * G + hh] * 1.4426950408889634f, keep, add);
+                    inv = keep / (L * keep + add);
+                }
                 *reinterpret_cast<uint2*>(out + orow * HD + d) = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
             } else {
                 *reinterpret_cast<float4*>(part_o + (orow * S + z) * HD + d) = acc;
@@ -542,7 +604,12 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
             if (!valid[i]) continue;
             const size_t orow = (size_t)tok[i] * H + head[i];
             if (S == 1) {
-                const float inv = 1.f / l[i];
+                float inv = 1.f;
+                if constexpr (WEIGHTS == 0) {
+                    float keep = 1.f, add = 0.f;
+                    if (ex.sink != nullptr) sink_terms(m[i], ex.sink[head[i]] * 1.4426950408889634f, keep, add);
+                    inv = keep / (l[i] * keep + add);
+                }
 #pragma unroll
                 for (int n = 0; n < ON; ++n)
                     *reinterpret_cast<uint32_t*>(out + orow * HD + n * 8 + 2 * tq) = pack_bf16(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
@@ -559,12 +626,22 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
 // Merge the pieces of a split sequence: maxima and sums are in the exp2 domain of the kernel above.
 template <int HD>
 __global__ void attention_mma_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                             bf16* __restrict__ out, int H, int S) {
+                                             bf16* __restrict__ out, int H, int S, const float* __restrict__ sink, int weights) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t orow = (size_t)blockIdx.x * H + blockIdx.y;
+    if (weights == 1) {                                  // sigmoid weights are not normalised: the pieces add up
+        for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+            float acc = 0.f;
+            for (int z = 0; z < S; ++z) acc += part_o[(orow * S + z) * HD + d];
+            out[orow * HD + d] = __float2bfloat16_rn(acc);
+        }
+        return;
+    }
     float M = -INFINITY;
     for (int z = 0; z < S; ++z) M = fmaxf(M, part_ml[(orow * S + z) * 2]);
+    float keep = 1.f, add = 0.f;
+    if (sink != nullptr) sink_terms(M, sink[blockIdx.y] * 1.4426950408889634f, keep, add);
     for (int d = threadIdx.x; d < HD; d += blockDim.x) {
         float L = 0.f, acc = 0.f;
         for (int z = 0; z < S; ++z) {
@@ -573,15 +650,15 @@ __global__ void attention_mma_combine_kernel(const float* __restrict__ part_o, c
             L += part_ml[(orow * S + z) * 2 + 1] * c;
             acc += part_o[(orow * S + z) * HD + d] * c;
         }
-        out[orow * HD + d] = __float2bfloat16_rn(acc / L);
+        out[orow * HD + d] = __float2bfloat16_rn(acc * keep / (L * keep + add));
     }
 }
 
-template <int HD, int WM, int WN, int NS, int SK = PAGE>
+template <int HD, int WM, int WN, int NS, int SK = PAGE, int WEIGHTS = 0>
 static int launch_mma(const bf16* q, int q_stride, bf16* out, const bf16* k, const bf16* v, const int* table, int bps,
                       const int* cu, const int* slots, const int* starts, const int* news, float* po, float* pml,
                       int n_seqs, int max_new, int n_rows, int H, int KV, float scale, int window, int S,
-                      const DecodeFuse& fuse, cudaStream_t stream) {
+                      const DecodeFuse& fuse, cudaStream_t stream, const AttentionExtra& ex = AttentionExtra{}) {
     const int G = H / KV;
     int Gp = 1;
     while (Gp < G) Gp <<= 1;
@@ -594,16 +671,16 @@ static int launch_mma(const bf16* q, int q_stride, bf16* out, const bf16* k, con
     if (WN > 1) smem = max(smem, (size_t)(2 * WN * ROWS + WN * ROWS * (HD + 8)) * sizeof(float));
     static bool configured = false;
     if (!configured) {
-        KL_CUDA(cudaFuncSetAttribute(attention_mma_kernel<HD, WM, WN, NS, SK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        KL_CUDA(cudaFuncSetAttribute(attention_mma_kernel<HD, WM, WN, NS, SK, WEIGHTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         // all of the SM's memory as shared memory: the kernel's data come through cp.async, and how many CTAs fit decides its speed
-        KL_CUDA(cudaFuncSetAttribute(attention_mma_kernel<HD, WM, WN, NS, SK>, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
+        KL_CUDA(cudaFuncSetAttribute(attention_mma_kernel<HD, WM, WN, NS, SK, WEIGHTS>, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
         configured = true;
     }
-    launch_kernel(attention_mma_kernel<HD, WM, WN, NS, SK>, grid, 32 * WM * WN, smem, stream, q, q_stride, out, k, v, table, bps, cu, slots,
-        starts, news, po, pml, H, KV, Gp, scale * 1.4426950408889634f, window, S, fuse);
+    launch_kernel(attention_mma_kernel<HD, WM, WN, NS, SK, WEIGHTS>, grid, 32 * WM * WN, smem, stream, q, q_stride, out, k, v, table, bps, cu, slots,
+        starts, news, po, pml, H, KV, Gp, scale * 1.4426950408889634f, window, S, fuse, ex);
     KL_LAUNCH_CHECK();
     if (S > 1 && !fuse.enabled) {
-        launch_kernel(attention_mma_combine_kernel<HD>, dim3(n_rows, H), HD <= 64 ? 32 : 64, 0, stream, po, pml, out, H, S);
+        launch_kernel(attention_mma_combine_kernel<HD>, dim3(n_rows, H), HD <= 64 ? 32 : 64, 0, stream, po, pml, out, H, S, ex.sink, WEIGHTS);
         KL_LAUNCH_CHECK();
     }
     return KL_OK;
@@ -670,6 +747,38 @@ KL_API int kl_attention_mma(const void* q, int q_stride, void* out, const void* 
     return attention_mma_dispatch(q, q_stride, out, k_cache, v_cache, block_table, blocks_per_seq, cu_tokens, seq_slots,
                                   seq_starts, seq_new, part_o, part_ml, n_seqs, max_new, n_rows, H, KV, hd, scale, window,
                                   splits, few_rows, none, stream);
+}
+
+// The same with the options of `AttentionExtra`: a sink per head (weights 0), sigmoid weights with a number per head (weights 1),
+// pooled rows (pool > 0: caches of block means [pages][KV][PAGE][hd] with a block table of their own, a window is needed).
+// Prefill layout, or with few_rows the four-warp decode layout on whole pages.
+KL_API int kl_attention_mma_extra(const void* q, int q_stride, void* out, const void* k_cache, const void* v_cache,
+                                  const int* block_table, int blocks_per_seq, const int* cu_tokens, const int* seq_slots,
+                                  const int* seq_starts, const int* seq_new, float* part_o, float* part_ml, int n_seqs,
+                                  int max_new, int n_rows, int H, int KV, int hd, float scale, int window, int splits,
+                                  int few_rows, const float* sink, const float* head_bias, int weights, const void* pool_k,
+                                  const void* pool_v, const int* pool_table, int pool_blocks_per_seq, int pool, cudaStream_t stream) {
+    if (n_seqs <= 0 || max_new <= 0) return KL_OK;
+    if (KV <= 0 || H % KV || splits < 1 || (weights != 0 && weights != 1)) return KL_ERR_BAD_SIZE;
+    if (splits > 1 && (part_o == nullptr || part_ml == nullptr)) return KL_ERR_BAD_SIZE;
+    if (q_stride % 2 || ((uintptr_t)q & 3)) return KL_ERR_BAD_ALIGN;
+    if (pool > 0 && (window <= 0 || pool_k == nullptr || pool_v == nullptr || pool_table == nullptr)) return KL_ERR_BAD_SIZE;
+    if (weights == 1 && sink != nullptr) return KL_ERR_BAD_SIZE;
+    DecodeFuse none;
+    memset(&none, 0, sizeof(none));
+    AttentionExtra ex;
+    ex.sink = sink; ex.head_bias = head_bias; ex.pool_k = (const bf16*)pool_k; ex.pool_v = (const bf16*)pool_v;
+    ex.pool_table = pool_table; ex.pool_blocks_per_seq = pool_blocks_per_seq; ex.pool = pool > 0 ? pool : 0;
+#define KL_MMAX(HD, WM, WN, W)                                                                                                   \
+    return launch_mma<HD, WM, WN, 2, PAGE, W>((const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,  \
+                                              block_table, blocks_per_seq, cu_tokens, seq_slots, seq_starts, seq_new, part_o,   \
+                                              part_ml, n_seqs, max_new, n_rows, H, KV, scale, window, splits, none, stream, ex)
+    if (hd == 128 && weights == 0) { if (few_rows) KL_MMAX(128, 1, 4, 0); else KL_MMAX(128, 4, 1, 0); }
+    if (hd == 128 && weights == 1) { if (few_rows) KL_MMAX(128, 1, 4, 1); else KL_MMAX(128, 4, 1, 1); }
+    if (hd == 64 && weights == 0) { if (few_rows) KL_MMAX(64, 1, 4, 0); else KL_MMAX(64, 4, 1, 0); }
+    if (hd == 64 && weights == 1) { if (few_rows) KL_MMAX(64, 1, 4, 1); else KL_MMAX(64, 4, 1, 1); }
+#undef KL_MMAX
+    return KL_ERR_BAD_SIZE;
 }
 
 // A whole decode step's attention in one kernel: one token per sequence, rows in sequence

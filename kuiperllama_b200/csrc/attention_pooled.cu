@@ -4,8 +4,8 @@
 // Query token t of slot s at position p sees
 //   * the keys j with 0 <= p - j < window (all keys up to p without a window), and
 //   * for every block b of `pool` positions that lies wholly before the window, (b + 1) pool - 1 <= p - window,
-//     the block's mean key and mean value (float32 rows that pool_blocks_kernel wrote when the block's last
-//     position arrived; a position that has left the window while its block is still incomplete is not seen).
+//     the block's mean key and mean value (rows in the cache's dtype that pool_blocks_kernel wrote, from 32-bit sums,
+//     when the block's last position arrived; a position that has left the window while its block is still incomplete is not seen).
 // Pooled rows and keys are treated alike: score = (q . k) * scale, and the weight of what is seen is either
 //   softmax over everything seen, optionally with a sink exp(sink[h]) in the denominator, or
 //   sigmoid(score + head_bias[h]), not normalised over the keys.
@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(AP_WARPS * 32)
 attention_pooled_kernel(const T* __restrict__ q, long long q_stride, T* __restrict__ out,
                         const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                         const int* __restrict__ block_table, int blocks_per_seq,
-                        const float* __restrict__ pool_k, const float* __restrict__ pool_v,
+                        const T* __restrict__ pool_k, const T* __restrict__ pool_v,
                         const int* __restrict__ pool_table, int pool_blocks_per_seq, int pool,
                         const int* __restrict__ positions, const int* __restrict__ token_slot,
                         int H, int KV, int hd, float scale, int window, int vd,
@@ -124,8 +124,8 @@ attention_pooled_kernel(const T* __restrict__ q, long long q_stride, T* __restri
             const size_t row0 = ((size_t)ptable[base / PAGE] * KV + g) * PAGE + (base % PAGE);
             const bool valid = base + lane < n_blocks;
             float s = 0.f;
-            if (valid) s = ap_dot<float>(pool_k + (row0 + lane) * (size_t)hd, q_s, hd) * scale;
-            ap_fold<float, PL, SIGMOID>(s, valid, 0, min(n_blocks - base, 32) - 1, pool_v + row0 * (size_t)vd, vd, vd, bias, m, l, acc);
+            if (valid) s = ap_dot<T>(pool_k + (row0 + lane) * (size_t)hd, q_s, hd) * scale;
+            ap_fold<T, PL, SIGMOID>(s, valid, 0, min(n_blocks - base, 32) - 1, pool_v + row0 * (size_t)vd, vd, vd, bias, m, l, acc);
         } else {
             const int base = (first_chunk + u - pool_chunks) * 32;      // 32 keys inside one page
             const size_t row0 = ((size_t)table[base / PAGE] * KV + g) * PAGE + (base % PAGE);
@@ -177,7 +177,7 @@ attention_pooled_kernel(const T* __restrict__ q, long long q_stride, T* __restri
 template <typename T>
 __global__ void __launch_bounds__(128)
 pool_blocks_kernel(const T* __restrict__ k_cache, const T* __restrict__ v_cache, const int* __restrict__ block_table, int blocks_per_seq,
-                   float* __restrict__ pool_k, float* __restrict__ pool_v, const int* __restrict__ pool_table, int pool_blocks_per_seq,
+                   T* __restrict__ pool_k, T* __restrict__ pool_v, const int* __restrict__ pool_table, int pool_blocks_per_seq,
                    int pool, const int* __restrict__ seq_slots, const int* __restrict__ seq_starts, const int* __restrict__ seq_new,
                    int KV, int hd, int vd) {
     pdl_launch_dependents();
@@ -196,7 +196,7 @@ pool_blocks_kernel(const T* __restrict__ k_cache, const T* __restrict__ v_cache,
         float sum = 0.f;
         for (int j = 0; j < pool; ++j)
             sum += to_f32(src[cache_row_offset(block_table, blocks_per_seq, slot, b * pool + j, g, KV, width) + e]);
-        (key ? pool_k : pool_v)[prow * (size_t)width + e] = sum / (float)pool;
+        (key ? pool_k : pool_v)[prow * (size_t)width + e] = from_f32<T>(sum / (float)pool);
     }
 }
 
@@ -205,10 +205,10 @@ pool_blocks_kernel(const T* __restrict__ k_cache, const T* __restrict__ v_cache,
 using namespace kl;
 
 // q: rows of q_stride elements, head h at column h * hd.  out: [tokens, H * vd].  Caches [pages, KV, PAGE, hd] and
-// [pages, KV, PAGE, vd]; pooled rows float32 in pages of their own (pool <= 0: none).  weights: 0 softmax (sink float32 [H] or
+// [pages, KV, PAGE, vd]; pooled rows in the same dtype in pages of their own (pool <= 0: none).  weights: 0 softmax (sink float32 [H] or
 // null), 1 sigmoid (head_bias float32 [H] or null).
 KL_API int kl_attention_pooled(const void* q, long long q_stride, void* out, const void* k_cache, const void* v_cache,
-                               const int* block_table, int blocks_per_seq, const float* pool_k, const float* pool_v,
+                               const int* block_table, int blocks_per_seq, const void* pool_k, const void* pool_v,
                                const int* pool_table, int pool_blocks_per_seq, int pool, const int* positions,
                                const int* token_slot, int n_tokens, int H, int KV, int hd, float scale, int window, int vd,
                                const float* sink, const float* head_bias, int weights, int dtype, cudaStream_t stream) {
@@ -221,7 +221,7 @@ KL_API int kl_attention_pooled(const void* q, long long q_stride, void* out, con
     if (smem > 48 * 1024) return KL_ERR_BAD_SIZE;
 #define KL_AP(T, PL, SG)                                                                                                        \
     launch_kernel(attention_pooled_kernel<T, PL, SG>, grid, AP_WARPS * 32, smem, stream, (const T*)q, q_stride, (T*)out,        \
-                  (const T*)k_cache, (const T*)v_cache, block_table, blocks_per_seq, pool_k, pool_v, pool_table,                \
+                  (const T*)k_cache, (const T*)v_cache, block_table, blocks_per_seq, (const T*)pool_k, (const T*)pool_v, pool_table, \
                   pool_blocks_per_seq, pool, positions, token_slot, H, KV, hd, scale, window, vd, sink, head_bias)
 #define KL_AP_T(T)                                                                    \
     do {                                                                              \
@@ -237,8 +237,8 @@ KL_API int kl_attention_pooled(const void* q, long long q_stride, void* out, con
     return KL_OK;
 }
 
-KL_API int kl_pool_blocks(const void* k_cache, const void* v_cache, const int* block_table, int blocks_per_seq, float* pool_k,
-                          float* pool_v, const int* pool_table, int pool_blocks_per_seq, int pool, const int* seq_slots,
+KL_API int kl_pool_blocks(const void* k_cache, const void* v_cache, const int* block_table, int blocks_per_seq, void* pool_k,
+                          void* pool_v, const int* pool_table, int pool_blocks_per_seq, int pool, const int* seq_slots,
                           const int* seq_starts, const int* seq_new, int n_seqs, int max_new, int KV, int hd, int vd, int dtype,
                           cudaStream_t stream) {
     if (n_seqs <= 0) return KL_OK;
@@ -248,10 +248,10 @@ KL_API int kl_pool_blocks(const void* k_cache, const void* v_cache, const int* b
     const dim3 grid(n_seqs, per_seq, KV);
     if (dtype == KL_F32)
         launch_kernel(pool_blocks_kernel<float>, grid, 128, 0, stream, (const float*)k_cache, (const float*)v_cache, block_table,
-                      blocks_per_seq, pool_k, pool_v, pool_table, pool_blocks_per_seq, pool, seq_slots, seq_starts, seq_new, KV, hd, vd);
+                      blocks_per_seq, (float*)pool_k, (float*)pool_v, pool_table, pool_blocks_per_seq, pool, seq_slots, seq_starts, seq_new, KV, hd, vd);
     else if (dtype == KL_BF16)
         launch_kernel(pool_blocks_kernel<bf16>, grid, 128, 0, stream, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
-                      blocks_per_seq, pool_k, pool_v, pool_table, pool_blocks_per_seq, pool, seq_slots, seq_starts, seq_new, KV, hd, vd);
+                      blocks_per_seq, (bf16*)pool_k, (bf16*)pool_v, pool_table, pool_blocks_per_seq, pool, seq_slots, seq_starts, seq_new, KV, hd, vd);
     else
         return KL_ERR_BAD_DTYPE;
     KL_LAUNCH_CHECK();

@@ -482,7 +482,7 @@ def attention_pooled(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
                      value_dim: int, scale: float, window: int, *, weights: str = "softmax", sink: Optional[torch.Tensor] = None,
                      head_bias: Optional[torch.Tensor] = None, pooled=None) -> None:
     """out[t, h] = sum over what token t sees of weight * value: the keys of the last ``window`` positions (0: all) and, with
-    ``pooled`` (k, v float32 [pages, KV, PAGE, dim], block_table, pool), the mean key and value of every block of ``pool``
+    ``pooled`` (k, v [pages, KV, PAGE, dim] in the cache's dtype, block_table, pool), the mean key and value of every block of ``pool``
     positions that lies wholly before the window.  ``weights`` "softmax" (``sink``: float32 [heads] in the denominator) or
     "sigmoid" (sigmoid(score + head_bias[h]), not normalised).  ``q`` [tokens, >= heads * head_dim] with any row stride."""
     pk = pv = pt = None
@@ -502,7 +502,7 @@ def attention_pooled(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
         _need(b is None or (b.dtype == torch.float32 and b.is_contiguous() and b.numel() == H), f"attention_pooled: {name} must be float32 [heads]")
     _need(weights in ATTENTION_WEIGHTS, f"attention_pooled: weights {weights!r} (softmax, sigmoid)")
     if pool:
-        _need(window > 0 and pk.dtype == pv.dtype == torch.float32 and pk.is_contiguous() and pv.is_contiguous()
+        _need(window > 0 and pk.dtype == pv.dtype == k_cache.dtype and pk.is_contiguous() and pv.is_contiguous()
               and tuple(pk.shape[1:]) == (KV, PAGE, hd) and tuple(pv.shape[1:]) == (KV, PAGE, vd), "attention_pooled: pooled rows")
     _check(lib("attention_pooled").kl_attention_pooled(
         _ptr(q), ctypes.c_longlong(q.stride(0)), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
@@ -513,14 +513,14 @@ def attention_pooled(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, 
 
 def pool_blocks(k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor, pooled, step, num_kv_heads: int, head_dim: int,
                 value_dim: int) -> None:
-    """Writes the mean key and mean value (float32) of every block of ``pooled.pool`` positions whose last position is one of the
-    step's tokens, from the rows the cache holds."""
+    """Writes the mean key and mean value (32-bit sums, stored in the cache's dtype) of every block of ``pooled.pool`` positions
+    whose last position is one of the step's tokens, from the rows the cache holds."""
     _cuda(k_cache, v_cache, block_table, pooled.k, pooled.v, pooled.block_table)
     _i32(block_table, "block_table"); _i32(pooled.block_table, "pooled block_table")
     KV, hd, vd = num_kv_heads, head_dim, value_dim
     _need(k_cache.dtype == v_cache.dtype and k_cache.is_contiguous() and v_cache.is_contiguous() and tuple(k_cache.shape[1:]) == (KV, PAGE, hd)
           and tuple(v_cache.shape[1:]) == (KV, PAGE, vd), "pool_blocks: cache layout")
-    _need(pooled.k.dtype == pooled.v.dtype == torch.float32 and pooled.k.is_contiguous() and pooled.v.is_contiguous()
+    _need(pooled.k.dtype == pooled.v.dtype == k_cache.dtype and pooled.k.is_contiguous() and pooled.v.is_contiguous()
           and tuple(pooled.k.shape[1:]) == (KV, PAGE, hd) and tuple(pooled.v.shape[1:]) == (KV, PAGE, vd), "pool_blocks: pooled rows")
     _check(lib("attention_pooled").kl_pool_blocks(
         _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(pooled.k), _ptr(pooled.v), _ptr(pooled.block_table),
@@ -765,7 +765,7 @@ def latent_attention(qfull: torch.Tensor, out: torch.Tensor, cache: torch.Tensor
     each row's first ``value_dim`` columns; out [tokens, heads * value_dim].  bfloat16 with key and value sizes that are
     multiples of 16 and values up to 256 wide: the tensor-core kernel (attention_latent.cu); everything else: the plain one.
     ``window``: a token reads the keys of the last so many positions only (0: all)."""
-    if (qfull.dtype == torch.bfloat16 and LATENT_KERNEL == "mma" and not window and key_dim % 16 == 0 and value_dim % 16 == 0
+    if (qfull.dtype == torch.bfloat16 and LATENT_KERNEL == "mma" and key_dim % 16 == 0 and value_dim % 16 == 0
             and value_dim <= 256 and 3 * 64 * (key_dim + 8) * 2 <= 220 * 1024):
         _cuda(qfull, out, cache, block_table, sink)
         _i32(block_table, "block_table")
@@ -782,7 +782,7 @@ def latent_attention(qfull: torch.Tensor, out: torch.Tensor, cache: torch.Tensor
         _check(lib("attention_latent").kl_latent_attention_mma(
             _ptr(qfull), _ptr(out), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(step.cu_tokens), _ptr(step.seq_slots),
             _ptr(step.seq_starts), _ptr(step.seq_new), step.n_seqs, step.max_new, _ptr(sink), heads, key_dim, value_dim,
-            ctypes.c_float(scale), splits, _ptr(part), n, _stream()), "latent_attention_mma", 2 if splits > 1 else 1)
+            ctypes.c_float(scale), splits, _ptr(part), n, int(window or 0), _stream()), "latent_attention_mma", 2 if splits > 1 else 1)
         return
     attention_simt(qfull, heads * key_dim, out, cache, cache, block_table, step.positions, step.token_slot, step.n_tokens,
                    heads, 1, key_dim, scale, int(window or 0), value_dim=value_dim, sink=sink)
@@ -1383,11 +1383,19 @@ MMA_HEAD_DIMS = (64, 128)
 def attention_mma(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                   block_table: torch.Tensor, cu_tokens: torch.Tensor, seq_slots: torch.Tensor, seq_starts: torch.Tensor,
                   seq_new: torch.Tensor, n_seqs: int, max_new: int, n_rows: int, num_heads: int, num_kv_heads: int,
-                  head_dim: int, scale: float, window: int = 0, splits: int = 1, few_rows: bool = False) -> None:
+                  head_dim: int, scale: float, window: int = 0, splits: int = 1, few_rows: bool = False, *,
+                  sink: Optional[torch.Tensor] = None, weights: str = "softmax", head_bias: Optional[torch.Tensor] = None,
+                  pooled=None) -> None:
     """Tensor-core attention of a ragged batch over the paged cache (bfloat16, head sizes 64
     and 128).  ``few_rows``: the layout for one token per sequence; ``splits``: pieces each
-    sequence's pages are cut into."""
-    _cuda(q, out, k_cache, v_cache, block_table, cu_tokens, seq_slots, seq_starts, seq_new)
+    sequence's pages are cut into.  Options: ``sink`` (float32 [heads], joins the softmax's denominator), ``weights``
+    "sigmoid" (sigmoid(score + head_bias[h]), not normalised), ``pooled`` (block means in pages of their own, seen once the
+    whole block lies before the window)."""
+    extra = sink is not None or weights != "softmax" or head_bias is not None or pooled is not None
+    pk = pv = pt = None
+    if pooled is not None:
+        pk, pv, pt = pooled.k, pooled.v, pooled.block_table
+    _cuda(q, out, k_cache, v_cache, block_table, cu_tokens, seq_slots, seq_starts, seq_new, sink, head_bias, pk, pv, pt)
     for t, nm in ((block_table, "block_table"), (cu_tokens, "cu_tokens"), (seq_slots, "seq_slots"),
                   (seq_starts, "seq_starts"), (seq_new, "seq_new")):
         _i32(t, nm)
@@ -1401,6 +1409,21 @@ def attention_mma(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: to
     if splits > 1:
         po = torch.empty((n_rows, num_heads, splits, head_dim), dtype=torch.float32, device=q.device)
         pml = torch.empty((n_rows, num_heads, splits, 2), dtype=torch.float32, device=q.device)
+    if extra:
+        _i32(pt, "pooled block_table")
+        _need(weights in ATTENTION_WEIGHTS and (weights == "softmax" or sink is None), "attention_mma: softmax (with a sink) or sigmoid weights")
+        for b, name in ((sink, "sink"), (head_bias, "head_bias")):
+            _need(b is None or (b.dtype == torch.float32 and b.is_contiguous() and b.numel() == num_heads), f"attention_mma: {name} must be float32 [heads]")
+        if pooled is not None:
+            _need(window and pk.dtype == pv.dtype == torch.bfloat16 and pk.is_contiguous() and pv.is_contiguous()
+                  and tuple(pk.shape[1:]) == tuple(pv.shape[1:]) == (num_kv_heads, PAGE, head_dim), "attention_mma: pooled rows")
+        _check(lib("attention_mma").kl_attention_mma_extra(
+            _ptr(q), q_stride, _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+            _ptr(cu_tokens), _ptr(seq_slots), _ptr(seq_starts), _ptr(seq_new), _ptr(po), _ptr(pml), n_seqs, max_new, n_rows,
+            num_heads, num_kv_heads, head_dim, ctypes.c_float(scale), int(window or 0), splits, int(few_rows), _ptr(sink),
+            _ptr(head_bias), ATTENTION_WEIGHTS[weights], _ptr(pk), _ptr(pv), _ptr(pt), 0 if pt is None else pt.shape[1],
+            0 if pooled is None else int(pooled.pool), _stream()), "attention_mma", 2 if splits > 1 else 1)
+        return
     _check(lib("attention_mma").kl_attention_mma(
         _ptr(q), q_stride, _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
         _ptr(cu_tokens), _ptr(seq_slots), _ptr(seq_starts), _ptr(seq_new), _ptr(po), _ptr(pml), n_seqs, max_new, n_rows,

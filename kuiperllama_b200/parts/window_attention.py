@@ -29,13 +29,16 @@ class WindowAttentionMixer(Mixer):
 
     One product makes q | k | v; ``ops.qk_prepare`` does bias, rotation, norm and the cache write in one kernel;
     ``ops.pool_blocks`` writes the means of the blocks that the step completes.  Softmax without pooled blocks
-    runs on the attention kernels of ``AttentionMixer`` where they take the sizes (bfloat16, equal key and value
-    sizes of 64 or 128, no sink: the tensor cores); everything else on the plain kernels.
+    runs on the attention kernels of ``AttentionMixer`` where they take the sizes; a sink, sigmoid weights and pooled blocks
+    are options of the windowed tensor-core kernel (bfloat16, equal key and value sizes of 64 or 128, groups of up to 16
+    heads); everything else runs on the plain kernels.
 
     Spec: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``, ``value_dim``, ``scale``, ``window``, ``values``
     ("own" | "keys"), ``weights`` ("softmax" | "sigmoid"), ``pool`` (None), ``head_norm`` (None | {"eps"}), ``names``
     (q, k, o and optionally v, q_bias, k_bias, v_bias, q_norm, k_norm, sink, head_bias).  KuiperLLama's attention is
     the unbiased causal softmax over every earlier key (kuiper/source/model/llama3.cpp:610-639, mha_kernel.cu:61,74-106)."""
+
+    KERNEL = "mma"                # "simt": the plain kernels also for bfloat16 (for comparisons)
 
     @classmethod
     def manifest(cls, spec: PartSpec, prefix: str) -> Dict[str, TensorDecl]:
@@ -121,6 +124,16 @@ class WindowAttentionMixer(Mixer):
         window = int(self.window or 0)
         if self.weights == "softmax" and not self.pool and self.sink is None and self.vd == self.hd:
             ops.attention(q, proj.stride(0), attn, cache.k, cache.v, cache.block_table, step, self.H, self.KV, self.hd, self.scale, window)
+        elif (dt == torch.bfloat16 and self.KERNEL == "mma" and self.vd == self.hd and self.hd in ops.MMA_HEAD_DIMS and self.H // self.KV <= 16
+              and proj.stride(0) % 2 == 0 and q.data_ptr() % 4 == 0):
+            # the tensor cores: sink, sigmoid weights and pooled rows are options of the windowed kernel
+            splits = 1
+            if step.is_decode:
+                splits = ops.decode_attention_splits(step.n_seqs, self.KV, self.hd, getattr(step, "context_class", 0))
+            ops.attention_mma(q, proj.stride(0), attn, cache.k, cache.v, cache.block_table, step.cu_tokens, step.seq_slots, step.seq_starts,
+                              step.seq_new, step.n_seqs, step.max_new, n, self.H, self.KV, self.hd, self.scale, window, splits,
+                              few_rows=step.is_decode, sink=self.sink, weights=self.weights, head_bias=self.head_bias,
+                              pooled=cache.pooled if self.pool else None)
         elif self.weights == "softmax" and not self.pool:
             ops.attention_simt(q, proj.stride(0), attn, cache.k, cache.v, cache.block_table, step.positions, step.token_slot, n,
                                self.H, self.KV, self.hd, self.scale, window, value_dim=self.vd, sink=self.sink)

@@ -11,7 +11,7 @@ repeats, a buffer larger than L2 written between repeats), and print the achieve
         fixes the number of pieces the decode attention cuts a sequence into, else the package's rule)
     python microbench.py prefill_step --shape 8b --layers 2 --tokens 2048
         (one prompt through a few layers, launched kernel by kernel: the case for a launch list)
-    python microbench.py prefill_step --design terolix --shape 1b --layers 4 --tokens 2048     (another architecture; also munadra, bededra)
+    python microbench.py prefill_step --design terolix --shape 1b --layers 4 --tokens 2048     (another architecture; also munadra, bededra, dofevik)
 
 It is also the small case that profiler captures of single kernels are taken on.
 """
@@ -73,6 +73,11 @@ def _model_config(args, positions: int) -> dict:
         if z is None:
             raise SystemExit("--design bededra has the shapes 1b and 8b")
         return bench.bededra_config(z["width"], args.layers, z["heads"], z["kv_heads"], z["head_dim"], 32000)
+    if args.design == "dofevik":
+        z = bench.COMPARE_SIZES.get({"1b": "1b", "8b": "8b-8-layers"}.get(args.shape, args.shape))
+        if z is None:
+            raise SystemExit("--design dofevik has the shapes 1b and 8b")
+        return bench.dofevik_config(z["width"], args.layers, z["heads"], z["kv_heads"], z["head_dim"], 32000)
     if args.design == "munadra":
         z = {"1b": bench.COMPARE_SIZES["1b"], "8b": bench.COMPARE_SIZES["8b-8-layers"]}.get(args.shape)
         if z is None:
@@ -157,7 +162,7 @@ def main(argv=None) -> int:
     ap.add_argument("kernel", choices=["gemm_skinny", "gemm_tcgen05", "attention_prefill", "attention_decode", "decode_step",
                                            "prefill_step"])
     ap.add_argument("--shape", default="8b", choices=["8b", "7b", "1b", "70b"], help="decode_step: which of bench.py's shapes")
-    ap.add_argument("--design", default="llama", choices=["llama", "terolix", "munadra", "bededra"],
+    ap.add_argument("--design", default="llama", choices=["llama", "terolix", "munadra", "bededra", "dofevik"],
                     help="decode_step, prefill_step: the Llama shape, or the Terolix model of that width (1b, 8b; layers in the order "
                          "minGRU, minGRU, attention, delta rule)")
     ap.add_argument("--layers", type=int, default=4, help="decode_step: layers of the model")
