@@ -22,9 +22,9 @@
 // of two warps on half pages (three stages of 16 KB at a head size of 128: four CTAs per SM),
 // taken where three per SM would leave CTAs for a second round.
 //
-// Options beyond that (`AttentionExtra`, all off for the Llama decoder): a sink per head in the softmax's
-// denominator (exp(sink[h]): no key, no value); WEIGHTS = 1: the weight of a visible key is
-// sigmoid(score + head_bias[h]), not normalised over the keys; and pooled rows: a second paged cache
+// Options beyond that (`AttentionExtra`; template parameter WEIGHTS = 0 compiles none of them in, which is what the Llama
+// decoder runs): WEIGHTS = 2: a sink per head in the softmax's denominator (exp(sink[h]): no key, no value); WEIGHTS = 1: the
+// weight of a visible key is sigmoid(score + head_bias[h]), not normalised over the keys; and with either, pooled rows: a second paged cache
 // whose row b holds the mean key and mean value of the positions b * pool .. (b + 1) * pool - 1 and is
 // seen by position p when the whole block lies before p's window, (b + 1) * pool - 1 <= p - window.  The
 // pooled rows are walked first, as units of their own (by the CTA of split 0), then the window's keys.
@@ -302,7 +302,7 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
         head[i] = g * G + hh;
         pos[i] = valid[i] ? start + tl : -1;
         lo[i] = (window > 0 && valid[i]) ? max(0, pos[i] - window + 1) : 0;
-        nb[i] = (ex.pool > 0 && valid[i]) ? lo[i] / ex.pool : 0;                  // pooled rows this row sees: blocks wholly before its window
+        nb[i] = (WEIGHTS != 0 && ex.pool > 0 && valid[i]) ? lo[i] / ex.pool : 0;  // pooled rows this row sees: blocks wholly before its window
         hbias[i] = (WEIGHTS == 1 && ex.head_bias != nullptr && valid[i]) ? ex.head_bias[head[i]] * 1.4426950408889634f : 0.f;
     }
     // pages this CTA reads
@@ -315,15 +315,15 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
     const int* table = block_table + (size_t)slot * blocks_per_seq;
     const int full_below = start + t0;                   // keys <= this are visible to every valid row (no window)
     // Pooled rows: the first PU units of the walk, taken by the CTA of split 0.
-    const int max_nb = ex.pool > 0 ? max(0, max_pos - window + 1) / ex.pool : 0;
-    const int PU = (ex.pool > 0 && z == 0) ? (max_nb + SK - 1) / SK : 0;
-    const int* ptable = ex.pool > 0 ? ex.pool_table + (size_t)slot * ex.pool_blocks_per_seq : nullptr;
+    const int max_nb = (WEIGHTS != 0 && ex.pool > 0) ? max(0, max_pos - window + 1) / ex.pool : 0;
+    const int PU = (WEIGHTS != 0 && ex.pool > 0 && z == 0) ? (max_nb + SK - 1) / SK : 0;
+    const int* ptable = (WEIGHTS != 0 && ex.pool > 0) ? ex.pool_table + (size_t)slot * ex.pool_blocks_per_seq : nullptr;
 
     // Units of SK keys this CTA reads: its pages, without what lies wholly behind the last position.
     const int u_begin = p_begin * UPP, u_end = min(p_end * UPP, max_pos / SK + 1);
     // `unit` counts from u_begin - PU: the pooled units come first (their index below u_begin), then the keys' units.
     auto issue = [&](int unit, int st) {
-        if (unit < u_begin) {
+        if (WEIGHTS != 0 && unit < u_begin) {
             const int pu = unit - (u_begin - PU);
             const size_t off = (((size_t)ptable[pu / UPP] * KV + g) * PAGE + (pu % UPP) * SK) * HD;
             load_keys<HD, THREADS, SK>(k_stage + st * SK * HD, ex.pool_k + off);
@@ -404,7 +404,7 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
     }
     for (int pi = w_begin; pi < u_end; ++pi) {
         const int st = (pi - w_begin) % NS;
-        const bool pooled = pi < u_begin;                // a unit of block means: row index = block index
+        const bool pooled = WEIGHTS != 0 && pi < u_begin;    // a unit of block means: row index = block index
         if (next < u_end) { issue(next, (next - w_begin) % NS); ++next; } else cp_async_commit();
         cp_async_wait<NS - 1>();                         // all but the NS - 1 newest groups: unit pi has landed
         __syncthreads();
@@ -540,7 +540,8 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
             const size_t orow = (size_t)(row0 + tl) * H + (g * G + hh);
             if (S == 1) {
                 float inv = 1.f;
-                if constexpr (WEIGHTS == 0) {
+                if constexpr (WEIGHTS == 0) inv = 1.f / L;
+                if constexpr (WEIGHTS == 2) {
                     float keep = 1.f, add = 0.f;
                     if (ex.sink != nullptr) sink_terms(M, ex.sink[g * G + hh] * 1.4426950408889634f, keep, add);
                     inv = keep / (L * keep + add);
@@ -605,7 +606,8 @@ attention_mma_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict_
             const size_t orow = (size_t)tok[i] * H + head[i];
             if (S == 1) {
                 float inv = 1.f;
-                if constexpr (WEIGHTS == 0) {
+                if constexpr (WEIGHTS == 0) inv = 1.f / l[i];
+                if constexpr (WEIGHTS == 2) {
                     float keep = 1.f, add = 0.f;
                     if (ex.sink != nullptr) sink_terms(m[i], ex.sink[head[i]] * 1.4426950408889634f, keep, add);
                     inv = keep / (l[i] * keep + add);
@@ -680,7 +682,7 @@ static int launch_mma(const bf16* q, int q_stride, bf16* out, const bf16* k, con
         starts, news, po, pml, H, KV, Gp, scale * 1.4426950408889634f, window, S, fuse, ex);
     KL_LAUNCH_CHECK();
     if (S > 1 && !fuse.enabled) {
-        launch_kernel(attention_mma_combine_kernel<HD>, dim3(n_rows, H), HD <= 64 ? 32 : 64, 0, stream, po, pml, out, H, S, ex.sink, WEIGHTS);
+        launch_kernel(attention_mma_combine_kernel<HD>, dim3(n_rows, H), HD <= 64 ? 32 : 64, 0, stream, po, pml, out, H, S, ex.sink, WEIGHTS == 1 ? 1 : 0);
         KL_LAUNCH_CHECK();
     }
     return KL_OK;
@@ -773,9 +775,10 @@ KL_API int kl_attention_mma_extra(const void* q, int q_stride, void* out, const 
     return launch_mma<HD, WM, WN, 2, PAGE, W>((const bf16*)q, q_stride, (bf16*)out, (const bf16*)k_cache, (const bf16*)v_cache,  \
                                               block_table, blocks_per_seq, cu_tokens, seq_slots, seq_starts, seq_new, part_o,   \
                                               part_ml, n_seqs, max_new, n_rows, H, KV, scale, window, splits, none, stream, ex)
-    if (hd == 128 && weights == 0) { if (few_rows) KL_MMAX(128, 1, 4, 0); else KL_MMAX(128, 4, 1, 0); }
+    // template parameter: 1 = sigmoid weights, 2 = softmax with the options compiled in
+    if (hd == 128 && weights == 0) { if (few_rows) KL_MMAX(128, 1, 4, 2); else KL_MMAX(128, 4, 1, 2); }
     if (hd == 128 && weights == 1) { if (few_rows) KL_MMAX(128, 1, 4, 1); else KL_MMAX(128, 4, 1, 1); }
-    if (hd == 64 && weights == 0) { if (few_rows) KL_MMAX(64, 1, 4, 0); else KL_MMAX(64, 4, 1, 0); }
+    if (hd == 64 && weights == 0) { if (few_rows) KL_MMAX(64, 1, 4, 2); else KL_MMAX(64, 4, 1, 2); }
     if (hd == 64 && weights == 1) { if (few_rows) KL_MMAX(64, 1, 4, 1); else KL_MMAX(64, 4, 1, 1); }
 #undef KL_MMAX
     return KL_ERR_BAD_SIZE;

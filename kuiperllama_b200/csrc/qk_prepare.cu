@@ -11,9 +11,10 @@
 //     there is no value projection and the key heads as projected (with bias, before rotation and norm)
 //     are stored as values.
 //
-// A warp takes a head at a time through a row of shared memory, so the order of a head's sum of squares
-// depends on the head size only.  ExiledOfCode/KuiperLLama rotates whole heads from tables and has neither
-// biases nor norms on q and k (rope_kernel.cu:5-49, kuiper/source/model/llama3.cpp:610-639).
+// A token's heads are dealt to the CTAs of its grid row, a warp per head, and the head passes through a row of
+// shared memory, so the order of a head's sum of squares depends on the head size only.  ExiledOfCode/KuiperLLama
+// rotates whole heads from tables and has neither biases nor norms on q and k (rope_kernel.cu:5-49,
+// kuiper/source/model/llama3.cpp:610-639).
 #include "common.cuh"
 
 namespace kl {
@@ -49,7 +50,7 @@ qk_prepare_kernel(T* __restrict__ proj, long long ld, int q_col, int k_col, int 
     T* row = proj + (size_t)t * ld;
     const bool write = k_cache != nullptr;
     const int half = rot / 2;
-    for (int head = warp; head < H + KV; head += QKP_WARPS) {
+    for (int head = blockIdx.y * QKP_WARPS + warp; head < H + KV; head += gridDim.y * QKP_WARPS) {
         const bool is_q = head < H;
         if (!is_q && !write) continue;
         const int g = is_q ? head : head - H;
@@ -82,7 +83,7 @@ qk_prepare_kernel(T* __restrict__ proj, long long ld, int q_col, int k_col, int 
         __syncwarp();
     }
     if (write && v_col >= 0) {
-        for (int idx = threadIdx.x; idx < KV * vd; idx += blockDim.x) {
+        for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < KV * vd; idx += gridDim.y * blockDim.x) {
             const int g = idx / vd, e = idx - g * vd;
             T* dst = v_cache + cache_row_offset(block_table, blocks_per_seq, slot, pos, g, KV, vd);
             dst[e] = from_f32<T>(to_f32(row[(size_t)v_col + idx]) + (v_bias ? v_bias[idx] : 0.f));
@@ -107,9 +108,9 @@ KL_API int kl_qk_prepare(void* proj, long long ld, int q_col, int k_col, int v_c
     if ((k_cache == nullptr) != (v_cache == nullptr)) return KL_ERR_BAD_SIZE;
     if (v_col < 0 && vd != hd) return KL_ERR_BAD_SIZE;
     const size_t smem = (size_t)(rot + QKP_WARPS * hd) * sizeof(float);
-    if (smem > 48 * 1024) return KL_ERR_BAD_SIZE;
+    if (smem > 48 * 1024 || (H + KV + QKP_WARPS - 1) / QKP_WARPS > 65535) return KL_ERR_BAD_SIZE;
 #define KL_QKP(T)                                                                                                                  \
-    launch_kernel(qk_prepare_kernel<T>, n_tokens, QKP_WARPS * 32, smem, stream, (T*)proj, ld, q_col, k_col, v_col, q_bias, k_bias, \
+    launch_kernel(qk_prepare_kernel<T>, dim3(n_tokens, (H + KV + QKP_WARPS - 1) / QKP_WARPS), QKP_WARPS * 32, smem, stream, (T*)proj, ld, q_col, k_col, v_col, q_bias, k_bias, \
                   v_bias, inv_freq, rot, interleaved, head_norm, eps, q_norm_w, k_norm_w, positions, token_slot, block_table,      \
                   blocks_per_seq, (T*)k_cache, (T*)v_cache, H, KV, hd, vd)
     if (dtype == KL_F32) KL_QKP(float);

@@ -119,7 +119,7 @@ class LatentAttentionMixer(Mixer):
         else:
             qsrc, q_col = proj, self.inputs.column("q")
         # rows that belong to no sequence (a small step's padding) are not written by the kernels: keep them defined
-        make = torch.empty if n == step.n_seqs else torch.zeros
+        make = torch.zeros if n > sum(step.host_new) else torch.empty
         qfull = make((n, self.H * self.Dk), dtype=dt, device=dev)
         ops.latent_prepare(proj, q_col, self.inputs.column("dkv") if self.own else None, self.norm_weight, self.eps, self.inv_freq,
                            self.rot_dims, self.magnitude, self.interleaved, step.positions, step.token_slot, cache.block_table,

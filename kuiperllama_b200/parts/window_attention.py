@@ -118,7 +118,7 @@ class WindowAttentionMixer(Mixer):
         if self.pool and write:
             ops.pool_blocks(cache.k, cache.v, cache.block_table, cache.pooled, step, self.KV, self.hd, self.vd)
         # rows that belong to no sequence (a small step's padding) are not written by the kernels: keep them defined
-        make = torch.empty if n == step.n_seqs else torch.zeros
+        make = torch.zeros if n > sum(step.host_new) else torch.empty
         attn = make((n, self.H * self.vd), dtype=dt, device=proj.device)
         q = proj[:, q_col:q_col + self.H * self.hd]
         window = int(self.window or 0)
