@@ -19,8 +19,7 @@
 
 namespace kl {
 
-constexpr int QKP_WARPS = 8;
-constexpr int QKP_REGS = 4;             // elements of a head a lane fetches before the angles are known (heads up to 128)
+constexpr int QKP_WARPS = 4;
 
 template <typename T>
 __global__ void __launch_bounds__(QKP_WARPS * 32)
@@ -41,17 +40,6 @@ qk_prepare_kernel(T* __restrict__ proj, long long ld, int q_col, int k_col, int 
     const int pos = positions[t];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float* buf = smem + rot + (size_t)warp * hd;        // [hd] per warp
-    // The warp's first head is requested before the angles are made, so that its way from memory overlaps their arithmetic.
-    T* row = proj + (size_t)t * ld;
-    const int head0 = blockIdx.y * QKP_WARPS + warp;
-    const bool early = head0 < H + KV && hd <= 32 * QKP_REGS;
-    T first[QKP_REGS];
-    if (early) {
-        const T* src0 = row + (head0 < H ? q_col + (size_t)head0 * hd : k_col + (size_t)(head0 - H) * hd);
-#pragma unroll
-        for (int r = 0; r < QKP_REGS; ++r)
-            if (lane + 32 * r < hd) first[r] = src0[lane + 32 * r];
-    }
     for (int i = threadIdx.x; i < rot / 2; i += blockDim.x) {
         float s, c;
         sincosf((float)pos * inv_freq[i], &s, &c);
@@ -59,6 +47,7 @@ qk_prepare_kernel(T* __restrict__ proj, long long ld, int q_col, int k_col, int 
         cs[2 * i + 1] = s;
     }
     __syncthreads();
+    T* row = proj + (size_t)t * ld;
     const bool write = k_cache != nullptr;
     const int half = rot / 2;
     for (int head = blockIdx.y * QKP_WARPS + warp; head < H + KV; head += gridDim.y * QKP_WARPS) {
@@ -68,22 +57,10 @@ qk_prepare_kernel(T* __restrict__ proj, long long ld, int q_col, int k_col, int 
         T* src = row + (is_q ? q_col + (size_t)g * hd : k_col + (size_t)g * hd);
         const float* bias = is_q ? q_bias : k_bias;
         T* vdst = (!is_q && v_col < 0) ? v_cache + cache_row_offset(block_table, blocks_per_seq, slot, pos, g, KV, vd) : nullptr;
-        if (early && head == head0) {
-#pragma unroll
-            for (int r = 0; r < QKP_REGS; ++r) {
-                const int i = lane + 32 * r;
-                if (i < hd) {
-                    const float x = to_f32(first[r]) + (bias ? bias[(size_t)g * hd + i] : 0.f);
-                    buf[i] = x;
-                    if (vdst != nullptr) vdst[i] = from_f32<T>(x);  // the values are the keys as projected
-                }
-            }
-        } else {
-            for (int i = lane; i < hd; i += 32) {
-                const float x = to_f32(src[i]) + (bias ? bias[(size_t)g * hd + i] : 0.f);
-                buf[i] = x;
-                if (vdst != nullptr) vdst[i] = from_f32<T>(x);      // the values are the keys as projected
-            }
+        for (int i = lane; i < hd; i += 32) {
+            const float x = to_f32(src[i]) + (bias ? bias[(size_t)g * hd + i] : 0.f);
+            buf[i] = x;
+            if (vdst != nullptr) vdst[i] = from_f32<T>(x);          // the values are the keys as projected
         }
         __syncwarp();
         for (int i = lane; i < half; i += 32) {
