@@ -67,6 +67,9 @@ struct GemmArgs {
     // no clamp when limit <= 0 (act_custom 0: silu(g) * u).
     int act_custom;
     float act_limit, act_alpha, act_shift;
+    // The plain epilogue's activation on a complete result in bfloat16 (grouped products, no k cuts): 0 none, 1 the
+    // squared relu max(y, 0)^2.
+    int act_plain;
 };
 
 // Tile order for tokens-as-rows: all the feature tiles of a group of TC_GROUP_M token tiles
@@ -86,12 +89,25 @@ __device__ __forceinline__ void tile_of(int id, int tiles_m, int tiles_n, int& t
 // division takes a slow path whenever exp(-g) overflows, and this runs 16,384 times per tile beside
 // the products).  For g far below zero the denominator is huge or infinite and the quotient 0, as it should be.
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+__device__ __forceinline__ float plain_act(const GemmArgs& args, float y) {
+    if (args.act_plain != 1) return y;
+    y = fmaxf(y, 0.f);
+    return y * y;
+}
 __device__ __forceinline__ float gated_mul(const GemmArgs& args, float g, float u) {
     if (!args.act_custom) return silu_mul(g, u);
     if (args.act_limit > 0.f) { g = fminf(g, args.act_limit); u = fminf(fmaxf(u, -args.act_limit), args.act_limit); }
     return __fdividef(g, 1.0f + __expf(-args.act_alpha * g)) * (u + args.act_shift);
 }
 
+// The squared relu on 32 accumulator columns in place.
+__device__ __forceinline__ void relu2_chunk(uint32_t (&r)[32]) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        const float x = fmaxf(__uint_as_float(r[j]), 0.f);
+        r[j] = __float_as_uint(x * x);
+    }
+}
 // Tokens-as-rows: 32 accumulator columns of one token row to the output (columns n0 .. n0 + 31).
 __device__ __forceinline__ void store_row_chunk(const GemmArgs& args, int row, int n0, const uint32_t (&r)[32]) {
     const bool full_n = n0 + 32 <= args.rows_b;
@@ -383,7 +399,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
                             if (token0 + j < args.rows_b)
-                                outb[(size_t)(token0 + j) * args.ld_out + row] = __float2bfloat16_rn(__uint_as_float(r[j]) * inv_rms[c + j]);
+                                outb[(size_t)(token0 + j) * args.ld_out + row] = __float2bfloat16_rn(plain_act(args, __uint_as_float(r[j]) * inv_rms[c + j]));
                     }
                 }
             }
@@ -472,6 +488,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                         for (int j = 0; j < 32; ++j) r[j] = 0u;
                     }
+                    if (args.act_plain == 1) relu2_chunk(r);
                     if (row < args.rows_a) store_row_chunk(args, row, n0, r);
                 }
             }
@@ -746,12 +763,13 @@ KL_API int kl_gemm_tcgen05(const void* a, long long lda, const void* w, long lon
 // every tile of 128 places lies in one group (tile_group[tile], -1: skipped; M = tiles * 128 places).
 // w holds `groups` matrices of n_rows rows each, one after the other.  gated: a group's rows alternate
 // 64 gate rows and 64 up rows and the result has n_rows / 2 columns, with the activation of
-// (limit, alpha, shift) (see GemmArgs).  Single CTAs on tiles of 128 x 256.
+// (limit, alpha, shift) (see GemmArgs).  act: the plain epilogue's activation (0 none, 1 squared relu).  Single CTAs on
+// tiles of 128 x 256.
 KL_API int kl_gemm_tcgen05_grouped(const void* a, long long lda, const void* w, long long ldw, void* out, long long ldo, int M,
                                    int n_rows, int K, int groups, const int* tile_group, int gated, float limit, float alpha,
-                                   float shift, int* status, cudaStream_t stream) {
+                                   float shift, int act, int* status, cudaStream_t stream) {
     if (M <= 0 || n_rows <= 0 || groups <= 0) return KL_OK;
-    if (M % TC_BM || tile_group == nullptr || (gated && n_rows % 128)) return KL_ERR_BAD_SIZE;
+    if (M % TC_BM || tile_group == nullptr || (gated && n_rows % 128) || (act != 0 && (act != 1 || gated))) return KL_ERR_BAD_SIZE;
     if (!aligned_operand(a, lda, K) || !aligned_operand(w, ldw, K)) return KL_ERR_BAD_ALIGN;
     if ((long long)groups * n_rows > 0x7fffffffLL) return KL_ERR_BAD_SIZE;
     CUtensorMap ma, mb;
@@ -764,6 +782,7 @@ KL_API int kl_gemm_tcgen05_grouped(const void* a, long long lda, const void* w, 
     args.group_rows = n_rows;
     args.act_custom = gated;
     args.act_limit = limit; args.act_alpha = alpha; args.act_shift = shift;
+    args.act_plain = act;
     if ((long long)tiles_m * tiles_n > 0x7fffffffLL) return KL_ERR_BAD_SIZE;
     const int sms = kl::sm_count();
     if (sms <= 0) return KL_ERR_SETUP;
@@ -776,9 +795,9 @@ KL_API int kl_gemm_tcgen05_grouped(const void* a, long long lda, const void* w, 
 // every chosen group's weights stream once through the TMA ring.  gated as in kl_gemm_tcgen05_grouped.
 KL_API int kl_gemm_tcgen05_grouped_skinny(const void* a, long long lda, const void* w, long long ldw, void* out, long long ldo,
                                           int M, int n_rows, int K, int groups, const int* tile_group, int gated, float limit,
-                                          float alpha, float shift, int* status, cudaStream_t stream) {
+                                          float alpha, float shift, int act, int* status, cudaStream_t stream) {
     if (M <= 0 || n_rows <= 0 || groups <= 0) return KL_OK;
-    if (M % 16 || tile_group == nullptr || (gated && n_rows % 128)) return KL_ERR_BAD_SIZE;
+    if (M % 16 || tile_group == nullptr || (gated && n_rows % 128) || (act != 0 && (act != 1 || gated))) return KL_ERR_BAD_SIZE;
     if (!aligned_operand(a, lda, K) || !aligned_operand(w, ldw, K)) return KL_ERR_BAD_ALIGN;
     if ((long long)groups * n_rows > 0x7fffffffLL) return KL_ERR_BAD_SIZE;
     CUtensorMap ma, mb;
@@ -792,6 +811,7 @@ KL_API int kl_gemm_tcgen05_grouped_skinny(const void* a, long long lda, const vo
     args.group_rows = n_rows;
     args.act_custom = gated;
     args.act_limit = limit; args.act_alpha = alpha; args.act_shift = shift;
+    args.act_plain = act;
     const long long ctas = (long long)((n_rows + TC_BM - 1) / TC_BM) * list_tiles;
     if (ctas > 0x7fffffffLL) return KL_ERR_BAD_SIZE;
     dim3 grid((unsigned)ctas, 1, 1);

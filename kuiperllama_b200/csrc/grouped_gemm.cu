@@ -11,7 +11,7 @@
 //     mixture of experts: the list holds (token, choice) pairs.
 //
 // Epilogues: plain (optionally times sigmoid of one number per row and group, `row_gate`: a head's output gate on a
-// per-head projection), or a gated activation over weights that hold N gate rows followed by N up rows (or,
+// per-head projection; optionally an activation of the result, `act` 1: the squared relu max(y, 0)^2), or a gated activation over weights that hold N gate rows followed by N up rows (or,
 // `interleaved`, blocks of 64 gate rows each followed by the 64 up rows of the same outputs, N % 64 == 0):
 //     g = min(gate, limit), u = clamp(up, -limit, limit) (no clamp when limit <= 0),
 //     y = g * sigmoid(alpha * g) * (u + shift).
@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(GG_THREADS)
 grouped_gemm_kernel(const TI* __restrict__ A, long long lda, long long a_gs, const int* __restrict__ a_rows,
                     const TI* __restrict__ W, long long w_gs, TO* __restrict__ C, long long ldc, long long c_gs,
                     const int* __restrict__ tile_group, int M, int N, int K, float limit, float alpha, float shift, int interleaved,
-                    const TI* __restrict__ row_gate, long long gate_ld) {
+                    const TI* __restrict__ row_gate, long long gate_ld, int act) {
     pdl_launch_dependents();
     pdl_wait();
     constexpr int RM = BM / 16;                                   // rows per thread
@@ -105,6 +105,7 @@ grouped_gemm_kernel(const TI* __restrict__ A, long long lda, long long a_gs, con
             const int gn = n0 + tx * 4 + j;
             if (gn >= N) continue;
             float y = acc[0][i][j] * rg;
+            if (EPI != GG_GATED && act == 1) y = y > 0.f ? y * y : 0.f;      // the plain epilogue's activation: squared relu
             if (EPI == GG_GATED) {
                 float gt = y, up = acc[1][i][j];
                 if (limit > 0.f) { gt = fminf(gt, limit); up = fminf(fmaxf(up, -limit), limit); }
@@ -220,7 +221,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32)
 grouped_gemv_kernel(const bf16* __restrict__ A, long long lda, const int* __restrict__ a_rows, const int* __restrict__ live_rows,
                     const bf16* __restrict__ W, long long w_gs,
                     TO* __restrict__ C, long long ldc, const int* __restrict__ tile_group, int tile_rows, int N, int K,
-                    float limit, float alpha, float shift, int interleaved) {
+                    float limit, float alpha, float shift, int interleaved, int act) {
     pdl_launch_dependents();
     pdl_wait();
     const int g = tile_group[blockIdx.y];
@@ -304,7 +305,7 @@ grouped_gemv_kernel(const bf16* __restrict__ A, long long lda, const int* __rest
             } else {
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
-                    if (n0 + c < N) crow[n0 + c] = from_f32<TO>(acc[r][c]);
+                    if (n0 + c < N) crow[n0 + c] = from_f32<TO>(act == 1 ? (acc[r][c] > 0.f ? acc[r][c] * acc[r][c] : 0.f) : acc[r][c]);
             }
         }
     }
@@ -334,8 +335,9 @@ KL_API int kl_grouped_gemm_mma(const void* A, long long lda, long long a_gs, con
 // a_rows: the row of A every list place reads (-1: padding); or null: the place itself, where live_rows (if given) is not negative.
 KL_API int kl_grouped_gemv(const void* A, long long lda, const int* a_rows, const int* live_rows, const void* W, long long w_gs, void* C, long long ldc,
                            const int* tile_group, int tiles, int tile_rows, int N, int K, int gated, float limit, float alpha,
-                           float shift, int interleaved, int out_dtype, cudaStream_t stream) {
+                           float shift, int interleaved, int out_dtype, int act, cudaStream_t stream) {
     if (tiles <= 0 || N <= 0) return KL_OK;
+    if (act != 0 && (act != 1 || gated)) return KL_ERR_BAD_SIZE;
     if (K <= 0 || K % 8 || lda % 8 || tile_rows <= 0 || tile_group == nullptr || (interleaved && (!gated || N % 64))) return KL_ERR_BAD_SIZE;
     if ((((uintptr_t)A | (uintptr_t)W) & 15) != 0) return KL_ERR_BAD_ALIGN;
     if (tiles > 65535) return KL_ERR_BAD_SIZE;
@@ -343,7 +345,7 @@ KL_API int kl_grouped_gemv(const void* A, long long lda, const int* a_rows, cons
     const dim3 grid((N + per_cta - 1) / per_cta, tiles);
 #define KL_GV(TO, G)                                                                                                      \
     launch_kernel(grouped_gemv_kernel<TO, G>, grid, GV_WARPS * 32, 0, stream, (const bf16*)A, lda, a_rows, live_rows, (const bf16*)W, w_gs, \
-                  (TO*)C, ldc, tile_group, tile_rows, N, K, limit, alpha, shift, interleaved)
+                  (TO*)C, ldc, tile_group, tile_rows, N, K, limit, alpha, shift, interleaved, act)
     if (out_dtype == KL_BF16) { if (gated) KL_GV(bf16, true); else KL_GV(bf16, false); }
     else if (out_dtype == KL_F32) { if (gated) KL_GV(float, true); else KL_GV(float, false); }
     else return KL_ERR_BAD_DTYPE;
@@ -353,12 +355,14 @@ KL_API int kl_grouped_gemv(const void* A, long long lda, const int* a_rows, cons
 }
 
 // groups: the number of groups of a batched call (ignored for a routed one, whose tile_group has
-// `tiles` entries).  gated: 0 plain (W_g is [N, K]), 1 gated activation (W_g is [2 N, K]).
+// `tiles` entries).  gated: 0 plain (W_g is [N, K]), 1 gated activation (W_g is [2 N, K]).  act: the plain
+// epilogue's activation (0 none, 1 squared relu).
 KL_API int kl_grouped_gemm(const void* A, long long lda, long long a_gs, const int* a_rows, const void* W, long long w_gs,
                            void* C, long long ldc, long long c_gs, const int* tile_group, int tiles, int tile_rows, int groups,
                            int M, int N, int K, int gated, float limit, float alpha, float shift, int interleaved, const void* row_gate,
-                           long long gate_ld, int in_dtype, int out_dtype, cudaStream_t stream) {
+                           long long gate_ld, int in_dtype, int out_dtype, int act, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return KL_OK;
+    if (act != 0 && (act != 1 || gated)) return KL_ERR_BAD_SIZE;
     if (K <= 0 || (tile_rows != 16 && tile_rows != 64) || (interleaved && (!gated || N % 64))) return KL_ERR_BAD_SIZE;
     const int my = tile_group ? tiles : (M + tile_rows - 1) / tile_rows;
     const int gz = tile_group ? 1 : groups;
@@ -367,7 +371,7 @@ KL_API int kl_grouped_gemm(const void* A, long long lda, long long a_gs, const i
     const dim3 grid((N + GG_BN - 1) / GG_BN, my, gz);
 #define KL_GG(TI, TO, BM, EPI)                                                                                              \
     launch_kernel(grouped_gemm_kernel<TI, TO, BM, EPI>, grid, GG_THREADS, 0, stream, (const TI*)A, lda, a_gs, a_rows,         \
-                  (const TI*)W, w_gs, (TO*)C, ldc, c_gs, tile_group, M, N, K, limit, alpha, shift, interleaved, (const TI*)row_gate, gate_ld)
+                  (const TI*)W, w_gs, (TO*)C, ldc, c_gs, tile_group, M, N, K, limit, alpha, shift, interleaved, (const TI*)row_gate, gate_ld, act)
 #define KL_GG_BY(TI, TO)                                                                                                    \
     do {                                                                                                                    \
         if (tile_rows == 16) { if (gated) KL_GG(TI, TO, 16, GG_GATED); else KL_GG(TI, TO, 16, GG_PLAIN); }                  \

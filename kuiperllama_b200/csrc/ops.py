@@ -531,12 +531,22 @@ def pool_blocks(k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch
 # --------------------------------------------------------------------------- grouped products
 
 GROUPED_MMA_FROM_ROWS = 32       # rows from which a batched bfloat16 product takes the tensor-core kernel
+EPILOGUE_ACTIVATIONS = {"relu2": 1}     # what the grouped products' plain epilogues can apply themselves: max(y, 0)^2
+
+
+def _epilogue_activation(activation: Optional[str], gated) -> int:
+    if activation is None:
+        return 0
+    _need(gated is None and activation in EPILOGUE_ACTIVATIONS,
+          f"an ungated grouped product's epilogue applies one of {sorted(EPILOGUE_ACTIVATIONS)}, not {activation!r}")
+    return EPILOGUE_ACTIVATIONS[activation]
+
 
 
 def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, a_group_stride: int = 0, out_group_stride: int = 0,
                  rows: Optional[int] = None, a_rows: Optional[torch.Tensor] = None, tile_group: Optional[torch.Tensor] = None,
                  tile_rows: int = 64, gated: Optional[tuple] = None, interleaved: bool = False,
-                 row_gate: Optional[torch.Tensor] = None) -> None:
+                 row_gate: Optional[torch.Tensor] = None, activation: Optional[str] = None) -> None:
     """out_g = a_g @ w[g]^T for every group g, with ``w`` [groups, N (2 N if gated), K].
 
     Batched (``tile_group`` None): all ``rows`` rows for every group; group g reads the columns of ``a`` from
@@ -546,8 +556,10 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, a_group
     place.  ``gated`` = (limit, alpha, shift): the weights hold N gate rows then N up rows and the result
     is min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + shift); limit <= 0 clamps nothing.
     ``interleaved``: the gated weights alternate 64 gate rows and the 64 up rows of the same outputs instead.
-    ``row_gate`` [rows, groups] (batched, plain): group g's result of row t is multiplied by sigmoid(row_gate[t, g])."""
+    ``row_gate`` [rows, groups] (batched, plain): group g's result of row t is multiplied by sigmoid(row_gate[t, g]).
+    ``activation`` (plain): an activation of the result in the same kernel (``EPILOGUE_ACTIVATIONS``)."""
     _cuda(a, w, out, a_rows, tile_group)
+    act = _epilogue_activation(activation, gated)
     _i32(a_rows, "a_rows"); _i32(tile_group, "tile_group")
     _need(w.dim() == 3 and w.is_contiguous() and a.dtype == w.dtype, "grouped_gemm: weights must be contiguous [groups, N, K] in a's dtype")
     G, NW, K = w.shape
@@ -573,7 +585,7 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, a_group
         _cuda(row_gate)
         _need(tile_group is None and gated is None and row_gate.dtype == a.dtype and row_gate.dim() == 2 and row_gate.stride(1) == 1
               and row_gate.shape[0] >= M and row_gate.shape[1] == G, "grouped_gemm: row_gate is [rows, groups] of a batched plain product")
-    if (tile_group is None and gated is None and a.dtype == out.dtype == torch.bfloat16 and M >= GROUPED_MMA_FROM_ROWS and K % 8 == 0
+    if (tile_group is None and gated is None and not act and a.dtype == out.dtype == torch.bfloat16 and M >= GROUPED_MMA_FROM_ROWS and K % 8 == 0
             and a.stride(0) % 8 == 0 and a_group_stride % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
         # a prompt's per-head projections: the tensor cores
         _check(lib("grouped_gemm").kl_grouped_gemm_mma(
@@ -586,11 +598,12 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, a_group
         _ptr(out), ctypes.c_longlong(out.stride(0)), ctypes.c_longlong(out_group_stride), _ptr(tile_group), tiles, tile_rows, G, M, N, K,
         int(gated is not None), ctypes.c_float(lim), ctypes.c_float(alpha), ctypes.c_float(shift), int(bool(interleaved)), _ptr(row_gate),
         ctypes.c_longlong(0 if row_gate is None else row_gate.stride(0)), dtype_code(a.dtype),
-        dtype_code(out.dtype), _stream()), "grouped_gemm")
+        dtype_code(out.dtype), act, _stream()), "grouped_gemm")
 
 
 def grouped_gemv(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, a_rows: Optional[torch.Tensor], tile_group: torch.Tensor,
-                 tile_rows: int, gated: Optional[tuple] = None, interleaved: bool = False, live_rows: Optional[torch.Tensor] = None) -> None:
+                 tile_rows: int, gated: Optional[tuple] = None, interleaved: bool = False, live_rows: Optional[torch.Tensor] = None,
+                 activation: Optional[str] = None) -> None:
     """The routed product of ``grouped_gemm`` for few rows per group (a decode step): every group's weights are read once,
     a warp per four weight rows.  bfloat16 operands whose rows start on 16-byte boundaries.  ``a_rows`` None: a place reads
     its own row of ``a``, and ``live_rows`` (the list's rows, -1 at padding) says which places there are."""
@@ -608,7 +621,8 @@ def grouped_gemv(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, a_rows: Op
     _check(lib("grouped_gemm").kl_grouped_gemv(
         _ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(a_rows), _ptr(live_rows), _ptr(w), ctypes.c_longlong(NW * K), _ptr(out),
         ctypes.c_longlong(out.stride(0)), _ptr(tile_group), tiles, tile_rows, N, K, int(gated is not None), ctypes.c_float(lim),
-        ctypes.c_float(alpha), ctypes.c_float(shift), int(bool(interleaved)), dtype_code(out.dtype), _stream()), "grouped_gemv")
+        ctypes.c_float(alpha), ctypes.c_float(shift), int(bool(interleaved)), dtype_code(out.dtype), _epilogue_activation(activation, gated),
+        _stream()), "grouped_gemv")
 
 
 # --------------------------------------------------------------------------- mixture of experts
@@ -666,7 +680,7 @@ def moe_gather(x: torch.Tensor, list_rows: torch.Tensor) -> torch.Tensor:
 
 
 def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_group: torch.Tensor,
-                         gated: Optional[tuple] = None) -> None:
+                         gated: Optional[tuple] = None, activation: Optional[str] = None) -> None:
     """out[p] = a[p] @ w[g]^T on the tensor cores for a list of places sorted by group, every tile of 128 places
     in one group (``tile_group`` [places / 128], -1: skipped).  ``w`` [groups, rows, K] bfloat16; ``gated`` =
     (limit, alpha, shift): a group's rows alternate 64 gate rows and 64 up rows, out has rows / 2 columns."""
@@ -681,11 +695,11 @@ def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, ti
     _check(lib("gemm_tcgen05").kl_gemm_tcgen05_grouped(
         _ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(w), ctypes.c_longlong(K), _ptr(out), ctypes.c_longlong(out.stride(0)), M, R, K, G,
         _ptr(tile_group), int(gated is not None), ctypes.c_float(lim), ctypes.c_float(alpha), ctypes.c_float(shift),
-        _status_ptr(a.device), _stream()), "gemm_tcgen05_grouped")
+        _epilogue_activation(activation, gated), _status_ptr(a.device), _stream()), "gemm_tcgen05_grouped")
 
 
 def gemm_tcgen05_grouped_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_group: torch.Tensor,
-                                gated: Optional[tuple] = None) -> None:
+                                gated: Optional[tuple] = None, activation: Optional[str] = None) -> None:
     """The grouped product for few rows per group on the tensor cores, weights as tile rows: ``a`` holds the list's rows (tiles of
     16 places, ``tile_group`` [places / 16], -1: skipped); every chosen group's weights stream once through the TMA ring.
     Operands as for ``gemm_tcgen05_grouped``."""
@@ -700,7 +714,7 @@ def gemm_tcgen05_grouped_skinny(a: torch.Tensor, w: torch.Tensor, out: torch.Ten
     _check(lib("gemm_tcgen05").kl_gemm_tcgen05_grouped_skinny(
         _ptr(a), ctypes.c_longlong(a.stride(0)), _ptr(w), ctypes.c_longlong(K), _ptr(out), ctypes.c_longlong(out.stride(0)), M, R, K, G,
         _ptr(tile_group), int(gated is not None), ctypes.c_float(lim), ctypes.c_float(alpha), ctypes.c_float(shift),
-        _status_ptr(a.device), _stream()), "gemm_tcgen05_grouped_skinny")
+        _epilogue_activation(activation, gated), _status_ptr(a.device), _stream()), "gemm_tcgen05_grouped_skinny")
 
 
 def moe_combine(results: torch.Tensor, pair_pos: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:

@@ -96,10 +96,12 @@ class MoEFeedForward(FeedForward):
             stack = ops.interleave_gate_up if self.tensor_cores else (lambda g, u: torch.cat([g, u], dim=0))
             self.gate_up = torch.stack([stack(get("gate", e), get("up", e)) for e in range(self.E)]).contiguous()
         else:
-            # [experts, ff, hidden]: the up rows alone; the activation follows the product as a kernel of its own
+            # [experts, ff, hidden]: the up rows alone
             self.tensor_cores = dt == torch.bfloat16 and self.ff % 8 == 0 and self.hidden % 8 == 0
             self.gate_up = torch.stack([get("up", e) for e in range(self.E)]).contiguous()
             self.activation = None
+        # the up product's epilogue applies the ungated activation itself where it can; a kernel of its own follows otherwise
+        self.fused_act = self.act_kind if not self.gated and self.act_kind in ops.EPILOGUE_ACTIVATIONS else None
         self.down = torch.stack([get("down", e) for e in range(self.E)]).contiguous()
         self.shared_size = int(spec.get("shared_size") or 0)
         if self.shared_size:
@@ -107,7 +109,7 @@ class MoEFeedForward(FeedForward):
             self.shared_down = Linear(tensors[prefix + n["shared_down"]], runtime)
 
     def _activate(self, act: torch.Tensor) -> None:
-        if not self.gated:
+        if not self.gated and self.fused_act is None:
             ops.activation(act, act, self.act_kind)
 
     def forward(self, x, step: StepContext):
@@ -123,7 +125,7 @@ class MoEFeedForward(FeedForward):
             cap = list_rows.numel()
             rows = ops.moe_gather(x, list_rows)
             act = torch.empty((cap, self.ff), dtype=dt, device=dev)
-            ops.gemm_tcgen05_grouped(rows, self.gate_up, act, tile_group, gated=self.activation)
+            ops.gemm_tcgen05_grouped(rows, self.gate_up, act, tile_group, gated=self.activation, activation=self.fused_act)
             self._activate(act)
             res = torch.empty((cap, self.hidden), dtype=dt, device=dev)
             ops.gemm_tcgen05_grouped(act, self.down, res, tile_group)
@@ -136,18 +138,18 @@ class MoEFeedForward(FeedForward):
             if tile == 16 and self.tensor_cores and self.SKINNY == "tcgen05" and x.stride(0) % 8 == 0:
                 # a few rows per expert: the chosen experts' weights stream once through the tensor-core kernel's TMA ring
                 rows = ops.moe_gather(x, list_rows)
-                ops.gemm_tcgen05_grouped_skinny(rows, self.gate_up, act, tile_group, gated=self.activation)
+                ops.gemm_tcgen05_grouped_skinny(rows, self.gate_up, act, tile_group, gated=self.activation, activation=self.fused_act)
                 self._activate(act)
                 ops.gemm_tcgen05_grouped_skinny(act, self.down, res, tile_group)
             elif tile == 16 and dt == torch.bfloat16 and self.hidden % 8 == 0 and self.ff % 8 == 0 and x.stride(0) % 8 == 0:
                 # a few rows per expert: bound by reading the chosen experts' weights once
                 ops.grouped_gemv(x, self.gate_up, act, list_rows, tile_group, tile, gated=self.activation,
-                                 interleaved=self.tensor_cores and self.gated)
+                                 interleaved=self.tensor_cores and self.gated, activation=self.fused_act)
                 self._activate(act)
                 ops.grouped_gemv(act, self.down, res, None, tile_group, tile, live_rows=list_rows)
             else:
                 ops.grouped_gemm(x, self.gate_up, act, a_rows=list_rows, tile_group=tile_group, tile_rows=tile, gated=self.activation,
-                                 interleaved=self.tensor_cores and self.gated)
+                                 interleaved=self.tensor_cores and self.gated, activation=self.fused_act)
                 self._activate(act)
                 ops.grouped_gemm(act, self.down, res, a_rows=None, tile_group=tile_group, tile_rows=tile)
         out = torch.empty((2 if self.shared_size else 1, n, self.hidden), dtype=torch.float32, device=dev)

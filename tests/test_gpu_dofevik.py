@@ -295,6 +295,51 @@ def test_router_bias_and_weights_over_the_chosen():
         assert (E - 1) in choice[5].tolist()
 
 
+@pytest.mark.parametrize("E, K, ff, n, top", [(7, 200, 128, 9, 3), (5, 64, 24, 40, 2), (16, 256, 64, 700, 4), (3, 100, 18, 30, 1)])
+def test_the_experts_activation_inside_the_grouped_products(E, K, ff, n, top):
+    """Ungated experts: relu(W_up x)^2 from the epilogue of every form of the routed product (32-bit FMA tiles in both dtypes, a
+    warp per four weight rows, the tensor cores with tokens and with weights as tile rows) against the product and the
+    activation made apart."""
+    from kuiperllama_b200.csrc import ops
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(E * 10 + ff)
+    x = torch.randn(n, K, generator=g)
+    choice = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(n)]).int().to(dev)
+    up = torch.randn(E, ff, K, generator=g) / 8
+    relu2 = lambda t: torch.relu(t.double()) ** 2
+    for dt in (torch.float32, torch.bfloat16):
+        xd, w = x.to(dt).to(dev), up.to(dt).to(dev)
+        tol = 1e-5 if dt == torch.float32 else 3e-2
+        for tile in (16, 64):
+            pair_pos, list_rows, tile_group = ops.moe_plan(choice, E, tile)
+            live = (list_rows >= 0).cpu()
+            cap = list_rows.numel()
+            plain, fused = (torch.zeros(cap, ff, dtype=dt, device=dev) for _ in range(2))
+            ops.grouped_gemm(xd, w, plain, a_rows=list_rows, tile_group=tile_group, tile_rows=tile)
+            ops.grouped_gemm(xd, w, fused, a_rows=list_rows, tile_group=tile_group, tile_rows=tile, activation="relu2")
+            want = relu2(plain.cpu())[live]
+            assert float(want.abs().max()) > 0.05
+            assert torch.allclose(fused.cpu().double()[live], want, atol=tol, rtol=tol), (dt, tile)
+            if dt == torch.bfloat16 and K % 8 == 0 and tile == 16:
+                got = torch.zeros_like(fused)
+                ops.grouped_gemv(xd, w, got, list_rows, tile_group, 16, activation="relu2")
+                assert torch.allclose(got.cpu().double()[live], want, atol=tol, rtol=tol), "a warp per four weight rows"
+                rows = ops.moe_gather(xd, list_rows)
+                got = torch.zeros_like(fused)
+                ops.gemm_tcgen05_grouped_skinny(rows, w, got, tile_group, activation="relu2")
+                ops.check_status(torch.device(dev))
+                assert torch.allclose(got.cpu().double()[live], want, atol=tol, rtol=tol), "weights as tile rows"
+        if dt == torch.bfloat16 and K % 8 == 0:
+            pair_pos, list_rows, tile_group = ops.moe_plan(choice, E, 128)
+            live = (list_rows >= 0).cpu()
+            rows = ops.moe_gather(xd, list_rows)
+            plain, got = (torch.zeros(list_rows.numel(), ff, dtype=dt, device=dev) for _ in range(2))
+            ops.gemm_tcgen05_grouped(rows, w, plain, tile_group)
+            ops.gemm_tcgen05_grouped(rows, w, got, tile_group, activation="relu2")
+            ops.check_status(torch.device(dev))
+            assert torch.allclose(got.cpu().double()[live], relu2(plain.cpu())[live], atol=tol, rtol=tol), "tokens as tile rows"
+
+
 # ----------------------------------------------------------------------------- each mechanism alone, layer by layer
 
 @pytest.mark.parametrize("dtype", DTYPES)
