@@ -11,7 +11,7 @@
 //     mixture of experts: the list holds (token, choice) pairs.
 //
 // Epilogues: plain (optionally times sigmoid of one number per row and group, `row_gate`: a head's output gate on a
-// per-head projection; optionally an activation of the result, `act` 1: the squared relu max(y, 0)^2), or a gated activation over weights that hold N gate rows followed by N up rows (or,
+// per-head projection, or with `gate_elems` of one number per row and output, at column group * N + n of the gate's row; optionally an activation of the result, `act` 1: the squared relu max(y, 0)^2), or a gated activation over weights that hold N gate rows followed by N up rows (or,
 // `interleaved`, blocks of 64 gate rows each followed by the 64 up rows of the same outputs, N % 64 == 0):
 //     g = min(gate, limit), u = clamp(up, -limit, limit) (no clamp when limit <= 0),
 //     y = g * sigmoid(alpha * g) * (u + shift).
@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(GG_THREADS)
 grouped_gemm_kernel(const TI* __restrict__ A, long long lda, long long a_gs, const int* __restrict__ a_rows,
                     const TI* __restrict__ W, long long w_gs, TO* __restrict__ C, long long ldc, long long c_gs,
                     const int* __restrict__ tile_group, int M, int N, int K, float limit, float alpha, float shift, int interleaved,
-                    const TI* __restrict__ row_gate, long long gate_ld, int act) {
+                    const TI* __restrict__ row_gate, long long gate_ld, int act, int gate_elems) {
     pdl_launch_dependents();
     pdl_wait();
     constexpr int RM = BM / 16;                                   // rows per thread
@@ -99,12 +99,14 @@ grouped_gemm_kernel(const TI* __restrict__ A, long long lda, long long a_gs, con
         if (src[row] < 0) continue;
         TO* crow = Cg + (size_t)(m0 + row) * ldc;
         // one number per row and group on the result (a head's output gate), if given
-        const float rg = row_gate ? 1.0f / (1.0f + expf(-to_f32(row_gate[(size_t)(m0 + row) * gate_ld + g]))) : 1.0f;
+        // (with gate_elems: one number per row and output instead, at column g * N + n of the gate's row)
+        const float rg = (row_gate && !gate_elems) ? 1.0f / (1.0f + expf(-to_f32(row_gate[(size_t)(m0 + row) * gate_ld + g]))) : 1.0f;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int gn = n0 + tx * 4 + j;
             if (gn >= N) continue;
             float y = acc[0][i][j] * rg;
+            if (row_gate && gate_elems) y *= 1.0f / (1.0f + expf(-to_f32(row_gate[(size_t)(m0 + row) * gate_ld + (size_t)g * N + gn])));
             if (EPI != GG_GATED && act == 1) y = y > 0.f ? y * y : 0.f;      // the plain epilogue's activation: squared relu
             if (EPI == GG_GATED) {
                 float gt = y, up = acc[1][i][j];
@@ -136,7 +138,7 @@ constexpr int GM_TILE = 64, GM_LD = 72;
 __global__ void __launch_bounds__(128)
 grouped_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, long long a_gs, const bf16* __restrict__ W, long long w_gs,
                         bf16* __restrict__ C, long long ldc, long long c_gs, int M, int N, int K,
-                        const bf16* __restrict__ row_gate, long long gate_ld) {
+                        const bf16* __restrict__ row_gate, long long gate_ld, int gate_elems) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ __align__(16) bf16 As[GM_TILE][GM_LD];
@@ -183,18 +185,20 @@ grouped_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, long long a_g
     for (int i = 0; i < 2; ++i) {
         const int row = m0 + warp * 16 + (lane >> 2) + 8 * i;
         if (row >= M) continue;
-        const float rg = row_gate ? 1.0f / (1.0f + expf(-to_f32(row_gate[(size_t)row * gate_ld + g]))) : 1.0f;
+        const float rg = (row_gate && !gate_elems) ? 1.0f / (1.0f + expf(-to_f32(row_gate[(size_t)row * gate_ld + g]))) : 1.0f;
+        const bf16* erow = (row_gate && gate_elems) ? row_gate + (size_t)row * gate_ld + (size_t)g * N : nullptr;     // a gate number per output
+        auto eg = [&](int col) { return erow ? 1.0f / (1.0f + expf(-to_f32(erow[col]))) : 1.0f; };
         bf16* crow = Cg + (size_t)row * ldc;
         const bool pairs = (((uintptr_t)Cg | (uintptr_t)(ldc * 2)) & 3) == 0;      // two neighbours as one 4-byte store
 #pragma unroll
         for (int n = 0; n < 8; ++n) {
             const int col = n0 + n * 8 + 2 * (lane & 3);
             if (pairs && col + 1 < N) {
-                const __nv_bfloat162 v = __floats2bfloat162_rn(acc[n][2 * i] * rg, acc[n][2 * i + 1] * rg);
+                const __nv_bfloat162 v = __floats2bfloat162_rn(acc[n][2 * i] * rg * eg(col), acc[n][2 * i + 1] * rg * eg(col + 1));
                 *reinterpret_cast<__nv_bfloat162*>(crow + col) = v;
             } else {
-                if (col < N) crow[col] = __float2bfloat16_rn(acc[n][2 * i] * rg);
-                if (col + 1 < N) crow[col + 1] = __float2bfloat16_rn(acc[n][2 * i + 1] * rg);
+                if (col < N) crow[col] = __float2bfloat16_rn(acc[n][2 * i] * rg * eg(col));
+                if (col + 1 < N) crow[col + 1] = __float2bfloat16_rn(acc[n][2 * i + 1] * rg * eg(col + 1));
             }
         }
     }
@@ -319,14 +323,14 @@ using namespace kl;
 // offsets of A on 16-byte boundaries.
 KL_API int kl_grouped_gemm_mma(const void* A, long long lda, long long a_gs, const void* W, long long w_gs, void* C, long long ldc,
                                long long c_gs, int groups, int M, int N, int K, const void* row_gate, long long gate_ld,
-                               cudaStream_t stream) {
+                               int gate_elems, cudaStream_t stream) {
     if (M <= 0 || N <= 0 || groups <= 0) return KL_OK;
     if (K <= 0 || K % 8 || lda % 8 || a_gs % 8 || w_gs % 8) return KL_ERR_BAD_ALIGN;
     if ((((uintptr_t)A | (uintptr_t)W) & 15) != 0) return KL_ERR_BAD_ALIGN;
     const dim3 grid((N + GM_TILE - 1) / GM_TILE, (M + GM_TILE - 1) / GM_TILE, groups);
     if (grid.y > 65535 || grid.z > 65535) return KL_ERR_BAD_SIZE;
     launch_kernel(grouped_gemm_mma_kernel, grid, 128, 0, stream, (const bf16*)A, lda, a_gs, (const bf16*)W, w_gs, (bf16*)C, ldc, c_gs,
-                  M, N, K, (const bf16*)row_gate, gate_ld);
+                  M, N, K, (const bf16*)row_gate, gate_ld, gate_elems);
     KL_LAUNCH_CHECK();
     return KL_OK;
 }
@@ -360,7 +364,7 @@ KL_API int kl_grouped_gemv(const void* A, long long lda, const int* a_rows, cons
 KL_API int kl_grouped_gemm(const void* A, long long lda, long long a_gs, const int* a_rows, const void* W, long long w_gs,
                            void* C, long long ldc, long long c_gs, const int* tile_group, int tiles, int tile_rows, int groups,
                            int M, int N, int K, int gated, float limit, float alpha, float shift, int interleaved, const void* row_gate,
-                           long long gate_ld, int in_dtype, int out_dtype, int act, cudaStream_t stream) {
+                           long long gate_ld, int in_dtype, int out_dtype, int act, int gate_elems, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return KL_OK;
     if (act != 0 && (act != 1 || gated)) return KL_ERR_BAD_SIZE;
     if (K <= 0 || (tile_rows != 16 && tile_rows != 64) || (interleaved && (!gated || N % 64))) return KL_ERR_BAD_SIZE;
@@ -371,7 +375,7 @@ KL_API int kl_grouped_gemm(const void* A, long long lda, long long a_gs, const i
     const dim3 grid((N + GG_BN - 1) / GG_BN, my, gz);
 #define KL_GG(TI, TO, BM, EPI)                                                                                              \
     launch_kernel(grouped_gemm_kernel<TI, TO, BM, EPI>, grid, GG_THREADS, 0, stream, (const TI*)A, lda, a_gs, a_rows,         \
-                  (const TI*)W, w_gs, (TO*)C, ldc, c_gs, tile_group, M, N, K, limit, alpha, shift, interleaved, (const TI*)row_gate, gate_ld, act)
+                  (const TI*)W, w_gs, (TO*)C, ldc, c_gs, tile_group, M, N, K, limit, alpha, shift, interleaved, (const TI*)row_gate, gate_ld, act, gate_elems)
 #define KL_GG_BY(TI, TO)                                                                                                    \
     do {                                                                                                                    \
         if (tile_rows == 16) { if (gated) KL_GG(TI, TO, 16, GG_GATED); else KL_GG(TI, TO, 16, GG_PLAIN); }                  \

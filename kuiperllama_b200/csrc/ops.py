@@ -546,7 +546,7 @@ def _epilogue_activation(activation: Optional[str], gated) -> int:
 def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, a_group_stride: int = 0, out_group_stride: int = 0,
                  rows: Optional[int] = None, a_rows: Optional[torch.Tensor] = None, tile_group: Optional[torch.Tensor] = None,
                  tile_rows: int = 64, gated: Optional[tuple] = None, interleaved: bool = False,
-                 row_gate: Optional[torch.Tensor] = None, activation: Optional[str] = None) -> None:
+                 row_gate: Optional[torch.Tensor] = None, activation: Optional[str] = None, gate_elements: bool = False) -> None:
     """out_g = a_g @ w[g]^T for every group g, with ``w`` [groups, N (2 N if gated), K].
 
     Batched (``tile_group`` None): all ``rows`` rows for every group; group g reads the columns of ``a`` from
@@ -556,7 +556,8 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, a_group
     place.  ``gated`` = (limit, alpha, shift): the weights hold N gate rows then N up rows and the result
     is min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + shift); limit <= 0 clamps nothing.
     ``interleaved``: the gated weights alternate 64 gate rows and the 64 up rows of the same outputs instead.
-    ``row_gate`` [rows, groups] (batched, plain): group g's result of row t is multiplied by sigmoid(row_gate[t, g]).
+    ``row_gate`` [rows, groups] (batched, plain): group g's result of row t is multiplied by sigmoid(row_gate[t, g]); with
+    ``gate_elements`` it is [rows, groups * N] and every output has a number of its own, sigmoid(row_gate[t, g * N + n]).
     ``activation`` (plain): an activation of the result in the same kernel (``EPILOGUE_ACTIVATIONS``)."""
     _cuda(a, w, out, a_rows, tile_group)
     act = _epilogue_activation(activation, gated)
@@ -584,21 +585,22 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, a_group
     if row_gate is not None:
         _cuda(row_gate)
         _need(tile_group is None and gated is None and row_gate.dtype == a.dtype and row_gate.dim() == 2 and row_gate.stride(1) == 1
-              and row_gate.shape[0] >= M and row_gate.shape[1] == G, "grouped_gemm: row_gate is [rows, groups] of a batched plain product")
+              and row_gate.shape[0] >= M and row_gate.shape[1] == (G * N if gate_elements else G),
+              "grouped_gemm: row_gate is [rows, groups] (or [rows, groups * N]) of a batched plain product")
     if (tile_group is None and gated is None and not act and a.dtype == out.dtype == torch.bfloat16 and M >= GROUPED_MMA_FROM_ROWS and K % 8 == 0
             and a.stride(0) % 8 == 0 and a_group_stride % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
         # a prompt's per-head projections: the tensor cores
         _check(lib("grouped_gemm").kl_grouped_gemm_mma(
             _ptr(a), ctypes.c_longlong(a.stride(0)), ctypes.c_longlong(a_group_stride), _ptr(w), ctypes.c_longlong(NW * K), _ptr(out),
             ctypes.c_longlong(out.stride(0)), ctypes.c_longlong(out_group_stride), G, M, N, K, _ptr(row_gate),
-            ctypes.c_longlong(0 if row_gate is None else row_gate.stride(0)), _stream()), "grouped_gemm_mma")
+            ctypes.c_longlong(0 if row_gate is None else row_gate.stride(0)), int(bool(gate_elements)), _stream()), "grouped_gemm_mma")
         return
     _check(lib("grouped_gemm").kl_grouped_gemm(
         _ptr(a), ctypes.c_longlong(a.stride(0)), ctypes.c_longlong(a_group_stride), _ptr(a_rows), _ptr(w), ctypes.c_longlong(NW * K),
         _ptr(out), ctypes.c_longlong(out.stride(0)), ctypes.c_longlong(out_group_stride), _ptr(tile_group), tiles, tile_rows, G, M, N, K,
         int(gated is not None), ctypes.c_float(lim), ctypes.c_float(alpha), ctypes.c_float(shift), int(bool(interleaved)), _ptr(row_gate),
         ctypes.c_longlong(0 if row_gate is None else row_gate.stride(0)), dtype_code(a.dtype),
-        dtype_code(out.dtype), act, _stream()), "grouped_gemm")
+        dtype_code(out.dtype), act, int(bool(gate_elements)), _stream()), "grouped_gemm")
 
 
 def grouped_gemv(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, a_rows: Optional[torch.Tensor], tile_group: torch.Tensor,

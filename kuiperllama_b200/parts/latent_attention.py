@@ -130,9 +130,7 @@ class LatentAttentionMixer(Mixer):
         ops.latent_attention(qfull, lat, cache.k, cache.block_table, step, self.H, self.Dk, self.r, self.scale, self.sink,
                              window=int(self.window or 0))
         attn = torch.empty((n, self.H * self.dv), dtype=dt, device=dev)
-        # W_uv per head, and each head's result times sigmoid of its gate number in the same kernel
+        # W_uv per head, and each head's result times sigmoid of its gate number (or of every element's own) in the same kernel
         ops.grouped_gemm(lat, self.uv, attn, a_group_stride=self.r, out_group_stride=self.dv, rows=n, tile_rows=16 if n <= 16 else 64,
-                         row_gate=self.inputs.view("g") if self.gated and self.gate_kind == "head" else None)
-        if self.gated and self.gate_kind == "element":
-            ops.sigmoid_gate(attn, self.inputs.view("g"))
+                         row_gate=self.inputs.view("g") if self.gated else None, gate_elements=self.gate_kind == "element")
         return self.o.forward(attn, allow_partials=True)

@@ -340,6 +340,29 @@ def test_the_experts_activation_inside_the_grouped_products(E, K, ff, n, top):
             assert torch.allclose(got.cpu().double()[live], relu2(plain.cpu())[live], atol=tol, rtol=tol), "tokens as tile rows"
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_gate_number_per_output_inside_the_per_head_product(dtype):
+    """The batched product per head whose epilogue multiplies every output by sigmoid of a number of its own (the gate's row holds
+    them head by head): the 32-bit FMA tiles of 16 and 64 rows, and with many rows in bfloat16 the tensor-core form."""
+    from kuiperllama_b200.csrc import ops
+    dt, dev = getattr(torch, dtype), "cuda:0"
+    g = torch.Generator().manual_seed(2)
+    rnd = lambda *s: torch.randn(*s, generator=g)
+    tol = 1e-5 if dtype == "float32" else 2e-2
+    for rows, G, K, N, a_gs, o_gs, tile in ((37, 5, 12, 7, 20, 9, 16), (37, 5, 12, 7, 20, 9, 64), (150, 3, 40, 70, 48, 72, 64), (9, 4, 16, 24, 16, 24, 16)):
+        a, w = rnd(rows, G * a_gs).to(dt), (rnd(G, N, K) / 3).to(dt)
+        wide = rnd(rows, G * N + 11).to(dt).to(dev)                       # the gate's numbers are columns 3 .. of a wider matrix
+        gate = wide[:, 3:3 + G * N]
+        out = torch.zeros(rows, G * o_gs, dtype=dt, device=dev)
+        ops.grouped_gemm(a.to(dev), w.to(dev), out, a_group_stride=a_gs, out_group_stride=o_gs, rows=rows, tile_rows=tile, row_gate=gate,
+                         gate_elements=True)
+        want = torch.einsum("tgk,gnk->tgn", a.double().reshape(rows, G, a_gs)[..., :K], w.double())
+        want = want * torch.sigmoid(gate.cpu().double().reshape(rows, G, N))
+        got = out.cpu().double().reshape(rows, G, o_gs)
+        assert torch.allclose(got[..., :N], want, atol=2 * tol, rtol=tol), (rows, G, tile)
+        assert o_gs == N or float(got[..., N:].abs().max()) == 0.0
+
+
 # ----------------------------------------------------------------------------- each mechanism alone, layer by layer
 
 @pytest.mark.parametrize("dtype", DTYPES)
