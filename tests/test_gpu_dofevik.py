@@ -93,21 +93,30 @@ def _step(starts, news, dev="cuda:0"):
 # ----------------------------------------------------------------------------- the new kernels alone
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("aligned", [False, True])
 @pytest.mark.parametrize("H, G, d, dv, rot, interleaved, norm, weighted, own_v, biased",
                          [(6, 3, 16, 20, 8, True, True, False, True, True), (4, 2, 12, 12, 0, False, True, True, False, False),
                           (5, 5, 10, 6, 6, True, True, False, True, True), (8, 2, 64, 64, 32, False, False, False, True, False),
-                          (2, 1, 128, 128, 128, True, True, True, False, True), (3, 1, 18, 7, 4, False, False, False, True, True)])
-def test_bias_rotation_head_norm_and_cache_write(dtype, H, G, d, dv, rot, interleaved, norm, weighted, own_v, biased):
+                          (2, 1, 128, 128, 128, True, True, True, False, True), (3, 1, 18, 7, 4, False, False, False, True, True),
+                          (4, 2, 32, 64, 16, False, True, True, True, True), (3, 1, 256, 8, 64, True, True, False, True, True),
+                          (40, 8, 64, 64, 64, False, True, True, False, False), (7, 7, 8, 16, 6, True, True, True, True, True),
+                          (5, 1, 64, 64, 0, False, True, False, True, True)])
+def test_bias_rotation_head_norm_and_cache_write(dtype, aligned, H, G, d, dv, rot, interleaved, norm, weighted, own_v, biased):
     """``ops.qk_prepare`` alone on a ragged step over scattered pages: every option on and off, q and k columns that start
-    anywhere in a wider matrix, values of another size than the keys and values that are the keys as projected."""
+    anywhere in a wider matrix (or on 16-byte boundaries, where bfloat16 rows of head sizes 8, 16, ... 256 take the form with
+    eight elements a lane), values of another size than the keys and values that are the keys as projected."""
     from kuiperllama_b200.csrc import ops
     dt, dev = getattr(torch, dtype), "cuda:0"
     g = torch.Generator().manual_seed(H * 7 + d)
     starts, news = [5, 100, 0], [70, 1, 9]
     step = _step(starts, news)
     n = step.n_tokens
-    q_col, k_col, v_col = 8, 8 + H * d + 3, 8 + H * d + 3 + G * d + 5
+    gap = (lambda n: -n % 8) if aligned else (lambda n: 0)
+    q_col = 8
+    k_col = q_col + H * d + (gap(H * d) if aligned else 3)
+    v_col = k_col + G * d + (gap(G * d) if aligned else 5)
     width = v_col + G * dv + 2
+    width += gap(width)
     proj = torch.randn(n, width, generator=g).to(dt)
     f32 = lambda size, on=True: (0.5 * torch.randn(size, generator=g)).to(dev) if on else None
     qb, kb, vb = f32(H * d, biased), f32(G * d, biased), f32(G * dv, biased and own_v)
