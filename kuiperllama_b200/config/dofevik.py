@@ -114,7 +114,9 @@ class DofevikConfig:
                 rotation(at, m, "rot_dim")
             else:
                 H, G = positive_int(at, m, "heads"), positive_int(at, m, "kv_heads")
-                dim, vdim = positive_int(at, m, "dim"), positive_int(at, m, "vdim")
+                dim = positive_int(at, m, "dim")
+                # the values of "attention_2" are its keys: "vdim" may be left out there
+                vdim = dim if kind == "attention_2" and "vdim" not in m else positive_int(at, m, "vdim")
                 if H % G:
                     problems.append(f'{at}"heads" {H} is not a multiple of "kv_heads" {G}')
                 if kind == "attention":
@@ -172,7 +174,7 @@ class DofevikConfig:
                 "names": {"dq": "mix.dq", "dq_norm": "mix.dq.norm", "q": "mix.uq", "dkv": "mix.dkv", "dkv_norm": "mix.dkv.norm",
                           "uk": "mix.uk", "uv": "mix.uv", "g": "mix.g", "o": "mix.o"}}), self._rope(m["rot"], m["rot_dim"], "half")
         common = {"hidden_size": self.width, "num_heads": m["heads"], "num_kv_heads": m["kv_heads"], "head_dim": m["dim"],
-                  "value_dim": m["vdim"], "scale": float(m["scale"]), "window": window}
+                  "value_dim": m.get("vdim", m["dim"]), "scale": float(m["scale"]), "window": window}
         if kind == "attention":
             return PartSpec("window_attention", {
                 **common, "values": "own", "weights": "softmax", "head_norm": {"eps": self.norm_eps},

@@ -60,6 +60,14 @@ def test_round_trip_and_spec():
     assert spec.layers[1].feed_forward["shared_size"] is None and "shared_up" not in spec.layers[1].feed_forward["names"]
 
 
+def test_values_that_are_keys_need_no_size_of_their_own():
+    from kuiperllama_b200.config import config_from_dict
+    c = json.loads(json.dumps(CONFIGS["only_attention_2"]))
+    del c["layers"][0]["mixer"]["vdim"]
+    spec = config_from_dict(c).to_model_spec()
+    assert spec.layers[0].mixer["value_dim"] == spec.layers[0].mixer["head_dim"] == 12
+
+
 def test_linear_scaling_divides_every_frequency():
     from kuiperllama_b200.parts.position import rotary_inverse_frequencies
     plain = rotary_inverse_frequencies(8, 10000.0, None)
